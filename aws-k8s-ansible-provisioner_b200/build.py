@@ -28,7 +28,7 @@ NVCC_FLAGS = [
     "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr",
     "-Xcompiler", "-Wall", "-Xcudafe", "--diag_suppress=177",
 ]
-ENGINE_SOURCES = ["elementwise.cu", "elementwise_opt.cu", "gemm_simt.cu", "gemm_tc.cu", "gemm_pair.cu", "gemm_gateup.cu", "gemm_resid.cu", "gemm_mc.cu", "attn_decode.cu", "attn_prefill.cu", "attn_prefill_tc.cu", "sampling.cu", "chain.cu", "chain_cluster.cu",
+ENGINE_SOURCES = ["elementwise.cu", "elementwise_opt.cu", "gemm_simt.cu", "gemm_tc.cu", "gemm_pair.cu", "gemm_gateup.cu", "gemm_resid.cu", "gemm_mc.cu", "attn_decode.cu", "attn_prefill.cu", "attn_prefill_tc.cu", "sampling.cu", "chain.cu", "chain_cluster.cu", "gemm_any.cu", "resid_f32.cu", "attn_latent.cu", "moe_route.cu", "model_config.cu",
                   "engine.cu", "capi.cu"]
 
 
@@ -64,7 +64,7 @@ def _compile(src: str, obj: str, extra: list[str], verbose: bool) -> None:
         print(r.stdout, r.stderr, flush=True)
 
 
-def build(verbose: bool = False, force: bool = False, ptxas_info: bool = False) -> str:
+def build(verbose: bool = False, force: bool = False, ptxas_info: bool = False, library_only: bool = False) -> str:
     os.makedirs(BUILD, exist_ok=True)
     hdrs = _headers()
     extra = ["-Xptxas", "-v"] if ptxas_info else []
@@ -85,6 +85,8 @@ def build(verbose: bool = False, force: bool = False, ptxas_info: bool = False) 
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError("link failed:\n%s\n%s" % (r.stdout, r.stderr))
+    if library_only:   # callers that bind the C ABI in-process need neither the server nor the router binary
+        return LIB
     server_dir = os.path.join(CSRC, "server")
     if os.path.isdir(server_dir):
         srcs = sorted(os.path.join(server_dir, f) for f in os.listdir(server_dir) if f.endswith(".cpp"))

@@ -6,13 +6,24 @@ import os
 
 # B2_LIB_PATH: an alternative build of the same library (A/B measurements of one source change); never a fallback
 LIB_PATH = os.environ.get("B2_LIB_PATH") or os.path.join(os.path.dirname(os.path.abspath(__file__)), "libb2engine.so")
-ABI_VERSION = 2
-ARCH_QWEN3, ARCH_PHI3, ARCH_OPT = 0, 1, 2
+ABI_VERSION = 3
+ARCH_QWEN3, ARCH_PHI3, ARCH_OPT, ARCH_LERASUN = 0, 1, 2, 3
+MIXER_LATENT_ATTENTION = 1
+FF_NONE, FF_ROUTED_EXPERTS = 0, 1
 NUM_KERNEL_CLASSES = 12
 
 
 class B2Error(RuntimeError):
     pass
+
+
+class b2_layer_spec(C.Structure):
+    _fields_ = [
+        ("mixer", C.c_int32), ("heads", C.c_int32), ("dim", C.c_int32), ("rot_dim", C.c_int32), ("vdim", C.c_int32),
+        ("kv_rank", C.c_int32), ("kv_from", C.c_int32), ("rot_dims", C.c_int32), ("rot_base", C.c_float), ("scale", C.c_float),
+        ("ff", C.c_int32), ("ff_dim", C.c_int32), ("experts", C.c_int32), ("top", C.c_int32), ("groups", C.c_int32),
+        ("groups_keep", C.c_int32),
+    ]
 
 
 class b2_config(C.Structure):
@@ -23,6 +34,7 @@ class b2_config(C.Structure):
         ("block_size", C.c_int32), ("num_blocks", C.c_int32), ("gpu_mem_fraction", C.c_float), ("max_seqs", C.c_int32),
         ("max_batch_tokens", C.c_int32), ("use_cuda_graphs", C.c_int32), ("rope_inv_freq", C.POINTER(C.c_float)),
         ("arch", C.c_int32), ("rotary_dim", C.c_int32), ("max_positions", C.c_int32), ("sliding_window", C.c_int32),
+        ("layer_specs", C.POINTER(b2_layer_spec)), ("compute_f32", C.c_int32), ("logit_scale", C.c_float),
     ]
 
 
@@ -45,6 +57,7 @@ SIGNATURES = {
     "b2_engine_free": (None, [_P]),
     "b2_engine_info": (_I, [_P, C.POINTER(C.c_int64), C.POINTER(C.c_int64), C.POINTER(C.c_int64)]),
     "b2_seq_create": (_I, [_P, C.c_int32, _I32P]),
+    "b2_seq_reserve": (_I, [_P, C.c_int32, C.c_int32]),
     "b2_seq_free": (_I, [_P, C.c_int32]),
     "b2_seq_len": (_I, [_P, C.c_int32]),
     "b2_seq_truncate": (_I, [_P, C.c_int32, C.c_int32]),
@@ -52,6 +65,9 @@ SIGNATURES = {
     "b2_decode_step": (_I, [_P, C.c_int32, _I32P, _I32P, _I32P]),
     "b2_decode_run": (_I, [_P, C.c_int32, _I32P, C.c_int32, _I32P, C.POINTER(C.c_float)]),
     "b2_get_logits": (_I, [_P, C.c_int32, C.POINTER(C.c_float)]),
+    "b2_config_from_dir": (_I, [C.c_char_p, C.POINTER(b2_config), C.POINTER(b2_layer_spec), C.c_int32]),
+    "b2_prefill_logits": (_I, [_P, _I32P, _I32P, C.c_int32, _I32P, _I32P, C.c_int32, C.POINTER(C.c_float), _I32P]),
+    "b2_get_hidden_f32": (_I, [_P, C.c_int32, C.c_int32, C.POINTER(C.c_float)]),
     "b2_set_debug": (_I, [_P, C.c_int32]),
     "b2_get_hidden": (_I, [_P, C.c_int32, C.c_int32, C.POINTER(C.c_uint16)]),
     "b2_sample": (_I, [_P, C.c_int32, C.POINTER(b2_sampling), _I32P]),

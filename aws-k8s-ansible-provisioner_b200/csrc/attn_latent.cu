@@ -1,0 +1,278 @@
+// attn_latent.cu -- attention over a low-rank latent that all heads share, with a per-head softmax sink.
+//
+// Per token the cache holds ONE row: the normalised latent c [kv_rank] and one rotated key piece k_r [rot_dim] (not one
+// key and one value per head).  Head a's key would be (U_k[a] c | k_r) and its value U_v[a] c; instead of rebuilding them
+// for every cached token, the query is pulled through U_k once ("absorbed"):
+//     score(a, j)   = ((U_k[a]^T q_nope[a]) . c_j + q_rot[a] . k_r_j) * scale
+//     out_lat[a]    = sum_j p(a, j) c_j / (sum_j exp(score - m) + exp(sink[a] - m))
+// and U_v[a] is applied to out_lat afterwards (gemm_any.cu, one strided batch over the heads).  The pass therefore reads
+// kv_rank + rot_dim numbers per cached token for ALL heads, which is what makes this cache small.
+// The sink is one more term of the softmax denominator with no key and no value: unscaled, counted once.
+//
+// Everything here is fp32 arithmetic (scores, softmax, rotary angles in fp64 before the rounding, norms); the cache and
+// the operands handed on are fp32 or bf16.  Kernels:
+//   latent_finish     what follows the fused q | latent projection: rotary on the query's rotated piece, unit-RMS norm of
+//                     the latent with a plain gain, rotary on the shared key piece, cache row write
+//   latent_attention  one warp per (query token, head); a CTA's eight rows share 32-key tiles staged in shared memory; lane j
+//                     scores key j, then lane d accumulates latent dims d, d + 32, ...; the same kernel serves prompt
+//                     portions (64-token tiles over the block table) and decode steps (one row per sequence)
+#include "kernels.h"
+
+namespace b2 {
+
+namespace {
+
+template <typename T>
+__device__ __forceinline__ float ldf(const T* p);
+template <>
+__device__ __forceinline__ float ldf<float>(const float* p) { return *p; }
+template <>
+__device__ __forceinline__ float ldf<bf16>(const bf16* p) { return __bfloat162float(*p); }
+template <typename T>
+__device__ __forceinline__ void stf(T* p, float v);
+template <>
+__device__ __forceinline__ void stf<float>(float* p, float v) { *p = v; }
+template <>
+__device__ __forceinline__ void stf<bf16>(bf16* p, float v) { *p = __float2bfloat16_rn(v); }
+
+// (u, v) of pair i at position p turns by p * base^(-2 i / dims); angle formed in fp64, rounded once
+__device__ __forceinline__ void pair_cos_sin(int pos, int i, int dims, float base, float* c, float* s) {
+  const double f = exp2(-2.0 * (double)i / (double)dims * log2((double)base));
+  double sd, cd;
+  sincos((double)pos * f, &sd, &cd);
+  *c = (float)cd;
+  *s = (float)sd;
+}
+
+template <typename TX, typename TC>
+__global__ void __launch_bounds__(128) latent_finish_kernel(const float* __restrict__ qd, int ld, LatentGeom g, int has_kv,
+                                                            const float* __restrict__ latent_gain, const int32_t* __restrict__ positions,
+                                                            const int32_t* __restrict__ slots, TX* __restrict__ q_nope,
+                                                            float* __restrict__ q_rot, TC* __restrict__ cache) {
+  extern __shared__ float cs[];  // [rot_dims / 2] cos | sin
+  __shared__ float red[4];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int t = blockIdx.x;
+  const int pos = positions[t];
+  const int half = g.rot_dims / 2;
+  for (int i = threadIdx.x; i < half; i += 128) pair_cos_sin(pos, i, g.rot_dims, g.rot_base, &cs[i], &cs[half + i]);
+  __syncthreads();
+  const float* row = qd + (size_t)t * ld;
+  const int hw = g.dim + g.rot_dim;
+  for (int i = threadIdx.x; i < g.heads * g.dim; i += 128) {
+    const int a = i / g.dim, d = i - a * g.dim;
+    stf(q_nope + (size_t)t * g.heads * g.dim + i, row[a * hw + d]);
+  }
+  // rotated piece: pairs below rot_dims turn, the rest passes (one thread per pair; an odd last element passes alone)
+  const int pairs_per = (g.rot_dim + 1) / 2;
+  for (int i = threadIdx.x; i < g.heads * pairs_per; i += 128) {
+    const int a = i / pairs_per, p = i - a * pairs_per;
+    const float* src = row + a * hw + g.dim + 2 * p;
+    float* dst = q_rot + (size_t)t * g.heads * g.rot_dim + a * g.rot_dim + 2 * p;
+    const bool has_v = 2 * p + 1 < g.rot_dim;
+    const float u = src[0], v = has_v ? src[1] : 0.f;
+    if (p < half && has_v) {
+      dst[0] = u * cs[p] - v * cs[half + p];
+      dst[1] = v * cs[p] + u * cs[half + p];
+    } else {
+      dst[0] = u;
+      if (has_v) dst[1] = v;
+    }
+  }
+  if (!has_kv) return;
+  const int slot = slots[t];
+  if (slot < 0) return;
+  const float* lat = row + g.heads * hw;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < g.kv_rank; i += 128) ss = fmaf(lat[i], lat[i], ss);
+  ss = warp_sum(ss);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  ss = red[0] + red[1] + red[2] + red[3];
+  const float r = 1.0f / sqrtf(ss / (float)g.kv_rank + g.eps);
+  TC* crow = cache + (size_t)slot * (g.kv_rank + g.rot_dim);
+  for (int i = threadIdx.x; i < g.kv_rank; i += 128) stf(crow + i, lat[i] * r * latent_gain[i]);
+  const float* kr = lat + g.kv_rank;
+  for (int p = threadIdx.x; p < pairs_per; p += 128) {
+    const bool has_v = 2 * p + 1 < g.rot_dim;
+    const float u = kr[2 * p], v = has_v ? kr[2 * p + 1] : 0.f;
+    TC* dst = crow + g.kv_rank + 2 * p;
+    if (p < half && has_v) {
+      stf(dst, u * cs[p] - v * cs[half + p]);
+      stf(dst + 1, v * cs[p] + u * cs[half + p]);
+    } else {
+      stf(dst, u);
+      if (has_v) stf(dst + 1, v);
+    }
+  }
+}
+
+constexpr int LA_WARPS = 8, LA_KEYS = 32;
+
+// NR = ceil(kv_rank / 32): latent dims per lane
+template <typename TC, typename TX, int NR>
+__global__ void __launch_bounds__(LA_WARPS * 32) latent_attention_kernel(const float* __restrict__ q_abs, const float* __restrict__ q_rot,
+                                                                         const TC* __restrict__ cache, LatentGeom g,
+                                                                         const int32_t* __restrict__ block_table, int bt_stride, int block_size,
+                                                                         const PrefillTile* __restrict__ tiles, const int32_t* __restrict__ positions,
+                                                                         const int32_t* __restrict__ seq_lens, const float* __restrict__ sink,
+                                                                         TX* __restrict__ out_lat) {
+  extern __shared__ float sm[];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int R = g.kv_rank, D = g.kv_rank + g.rot_dim, SD = D | 1;  // odd row stride: lanes that walk down a column hit 32 banks
+  float* qs = sm;                       // [LA_WARPS][D]
+  float* ks = sm + LA_WARPS * D;        // [LA_KEYS][SD]
+  int q_row0, q_pos0, nrows, bt_row;
+  if (tiles != nullptr) {
+    const PrefillTile tl = tiles[blockIdx.x];
+    q_row0 = tl.q_row0; q_pos0 = tl.q_pos0; nrows = tl.nrows; bt_row = tl.bt_row;
+  } else {
+    q_row0 = blockIdx.x; q_pos0 = positions[blockIdx.x]; nrows = seq_lens[blockIdx.x] > 0 ? 1 : 0; bt_row = blockIdx.x;
+  }
+  const int total = nrows * g.heads;
+  const int first = blockIdx.y * LA_WARPS;
+  if (first >= total) return;
+  const int my = first + warp;
+  const bool active = my < total;
+  const int tok = active ? my / g.heads : 0, head = active ? my - tok * g.heads : 0;
+  const int my_pos = q_pos0 + tok;
+  const int last_row = min(first + LA_WARPS, total) - 1;
+  const int max_pos = q_pos0 + last_row / g.heads;
+  if (active) {
+    const float* qa = q_abs + ((size_t)(q_row0 + tok) * g.heads + head) * R;
+    const float* qr = q_rot + ((size_t)(q_row0 + tok) * g.heads + head) * g.rot_dim;
+    for (int d = lane; d < R; d += 32) qs[warp * D + d] = qa[d];
+    for (int d = lane; d < g.rot_dim; d += 32) qs[warp * D + R + d] = qr[d];
+  }
+  float o[NR];
+#pragma unroll
+  for (int i = 0; i < NR; ++i) o[i] = 0.f;
+  float m = -INFINITY, l = 0.f;
+  const int32_t* bt = block_table + (size_t)bt_row * bt_stride;
+  for (int k0 = 0; k0 <= max_pos; k0 += LA_KEYS) {
+    __syncthreads();  // previous tile consumed (and, first time, q staged)
+    const int nk = min(LA_KEYS, max_pos + 1 - k0);
+    for (int j = warp; j < nk; j += LA_WARPS) {
+      const int kp = k0 + j;
+      const TC* src = cache + ((size_t)bt[kp / block_size] * block_size + kp % block_size) * D;
+      for (int d = lane; d < D; d += 32) ks[j * SD + d] = ldf(src + d);
+    }
+    __syncthreads();
+    if (!active || k0 > my_pos) continue;
+    // lane j scores key k0 + j
+    float s = -INFINITY;
+    if (lane < nk && k0 + lane <= my_pos) {
+      const float* kr = ks + lane * SD;
+      const float* q = qs + warp * D;
+      float acc = 0.f;
+      for (int d = 0; d < D; ++d) acc = fmaf(q[d], kr[d], acc);
+      s = acc * g.scale;
+    }
+    const float m_new = fmaxf(m, warp_max(s));
+    const float p = s == -INFINITY ? 0.f : expf(s - m_new);
+    const float corr = m == -INFINITY ? 0.f : expf(m - m_new);
+    l = l * corr + warp_sum(p);
+#pragma unroll
+    for (int i = 0; i < NR; ++i) o[i] *= corr;
+    m = m_new;
+    for (int j = 0; j < nk; ++j) {
+      const float pj = __shfl_sync(0xffffffffu, p, j);
+      if (pj == 0.f) continue;  // warp-uniform
+      const float* c = ks + j * SD;
+#pragma unroll
+      for (int i = 0; i < NR; ++i) {
+        const int d = lane + 32 * i;
+        if (d < R) o[i] = fmaf(pj, c[d], o[i]);
+      }
+    }
+  }
+  if (!active) return;
+  // the sink: one more term of the denominator
+  const float sk = sink[head];
+  const float mf = fmaxf(m, sk);
+  const float corr = expf(m - mf);
+  const float den = l * corr + expf(sk - mf);
+  const float inv = corr / den;
+  TX* dst = out_lat + ((size_t)(q_row0 + tok) * g.heads + head) * R;
+#pragma unroll
+  for (int i = 0; i < NR; ++i) {
+    const int d = lane + 32 * i;
+    if (d < R) stf(dst + d, o[i] * inv);
+  }
+}
+
+template <typename TC, typename TX, int NR>
+int launch_la(const float* q_abs, const float* q_rot, const void* cache, const LatentGeom& g, const int32_t* block_table, int bt_stride,
+              int block_size, const PrefillTile* tiles, int ntiles, const int32_t* positions, const int32_t* seq_lens, const float* sink,
+              void* out_lat, int T, cudaStream_t s) {
+  const int D = g.kv_rank + g.rot_dim;
+  const size_t smem = ((size_t)LA_WARPS * D + (size_t)LA_KEYS * (D | 1)) * sizeof(float);
+  auto kern = latent_attention_kernel<TC, TX, NR>;
+  if (smem > 48 * 1024) {
+    static B2PerDeviceOnce once;
+    static size_t set_to = 0;
+    if (once.need() || smem > set_to) {
+      B2_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      set_to = smem;
+    }
+  }
+  const int rows_per_tile = tiles != nullptr ? 64 : 1;
+  dim3 grid(tiles != nullptr ? ntiles : T, (rows_per_tile * g.heads + LA_WARPS - 1) / LA_WARPS);
+  B2_CUDA_OK(b2_launch(kern, grid, dim3(LA_WARPS * 32), smem, s, q_abs, q_rot, (const TC*)cache, g, block_table, bt_stride, block_size, tiles,
+                       positions, seq_lens, sink, (TX*)out_lat));
+  return 0;
+}
+
+template <typename TC, typename TX>
+int launch_la_nr(int nr, const float* q_abs, const float* q_rot, const void* cache, const LatentGeom& g, const int32_t* block_table,
+                 int bt_stride, int block_size, const PrefillTile* tiles, int ntiles, const int32_t* positions, const int32_t* seq_lens,
+                 const float* sink, void* out_lat, int T, cudaStream_t s) {
+#define LA(N) return launch_la<TC, TX, N>(q_abs, q_rot, cache, g, block_table, bt_stride, block_size, tiles, ntiles, positions, seq_lens, sink, out_lat, T, s)
+  if (nr <= 1) LA(1);
+  if (nr <= 2) LA(2);
+  if (nr <= 4) LA(4);
+  if (nr <= 8) LA(8);
+  if (nr <= 16) LA(16);
+  LA(32);
+#undef LA
+}
+
+}  // namespace
+
+int launch_latent_finish(const float* qd, int ld, const LatentGeom& g, int has_kv, const float* latent_gain, const int32_t* positions,
+                         const int32_t* slots, void* q_nope, int x_f32, float* q_rot, void* cache, int cache_f32, int T, cudaStream_t s) {
+  if (T <= 0) return 0;
+  B2_REQUIRE(g.rot_dims >= 0 && g.rot_dims <= g.rot_dim && g.rot_dims % 2 == 0, "latent_finish: rot_dims %d must be even and <= rot_dim %d",
+             g.rot_dims, g.rot_dim);
+  B2_REQUIRE(x_f32 == cache_f32, "latent_finish: operands and cache have one element type");
+  const size_t smem = (size_t)std::max(g.rot_dims, 2) * sizeof(float);
+  if (x_f32)
+    B2_CUDA_OK(b2_launch(latent_finish_kernel<float, float>, dim3(T), dim3(128), smem, s, qd, ld, g, has_kv, latent_gain, positions, slots,
+                         (float*)q_nope, q_rot, (float*)cache));
+  else
+    B2_CUDA_OK(b2_launch(latent_finish_kernel<bf16, bf16>, dim3(T), dim3(128), smem, s, qd, ld, g, has_kv, latent_gain, positions, slots,
+                         (bf16*)q_nope, q_rot, (bf16*)cache));
+  return 0;
+}
+
+int launch_latent_attention(const float* q_abs, const float* q_rot, const void* cache, int cache_f32, const LatentGeom& g,
+                            const int32_t* block_table, int bt_stride, int block_size, const PrefillTile* tiles, int ntiles,
+                            const int32_t* positions, const int32_t* seq_lens, const float* sink, void* out_lat, int x_f32, int T,
+                            cudaStream_t s) {
+  if (T <= 0 || (tiles != nullptr && ntiles <= 0)) return 0;
+  B2_REQUIRE(g.kv_rank >= 1 && g.kv_rank <= 1024, "latent_attention: kv_rank %d outside [1, 1024]", g.kv_rank);
+  B2_REQUIRE(x_f32 == cache_f32, "latent_attention: operands and cache have one element type");
+  const size_t smem = ((size_t)LA_WARPS * (g.kv_rank + g.rot_dim) + (size_t)LA_KEYS * ((g.kv_rank + g.rot_dim) | 1)) * sizeof(float);
+  B2_REQUIRE(smem <= 200 * 1024, "latent_attention: kv_rank + rot_dim = %d needs %zu bytes of shared memory", g.kv_rank + g.rot_dim, smem);
+  const int nr = (g.kv_rank + 31) / 32;
+  if (cache_f32)
+    return launch_la_nr<float, float>(nr, q_abs, q_rot, cache, g, block_table, bt_stride, block_size, tiles, ntiles, positions, seq_lens, sink,
+                                      out_lat, T, s);
+  return launch_la_nr<bf16, bf16>(nr, q_abs, q_rot, cache, g, block_table, bt_stride, block_size, tiles, ntiles, positions, seq_lens, sink,
+                                  out_lat, T, s);
+}
+
+}  // namespace b2

@@ -78,6 +78,16 @@ struct LayerW {
   CUtensorMap tm_gu64;                  // 64-row box: gate rows and up rows of one SwiGLU tile (gemm_pair.cu)
 };
 
+// One layer of a layer-list family (Lerasun).  Operand-typed tensors (void*) are bf16, or fp32 when the engine computes in
+// fp32; gains, the sink, the router and its correction are always fp32.
+struct ListLayer {
+  b2_layer_spec sp;
+  int nq = 0, nqd = 0;        // rows of the fused q | latent projection: heads * (dim + rot_dim), + kv_rank + rot_dim when the layer has its own latent
+  int cache_region = -1;      // which cache region the layer attends over (its own, or layer kv_from's)
+  void *wqd = nullptr, *ukT = nullptr, *uv = nullptr, *wo = nullptr, *up = nullptr, *down = nullptr;
+  float *gain1 = nullptr, *gain2 = nullptr, *lat_gain = nullptr, *sink = nullptr, *router = nullptr, *corr = nullptr;
+};
+
 struct Seq {
   bool active = false;
   int len = 0;        // tokens whose K/V are in the cache
@@ -255,6 +265,29 @@ struct b2_engine {
   float* attn_scratch2 = nullptr;
   float* ssq = nullptr;  // [hidden / 16][64]: pieces of the next RMSNorm's sum of squares (gemm_resid.cu -> gemm_pair.cu)
   cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
+
+  // Cache regions: one per layer and K/V for the GQA families, one per layer that stores a latent for the layer-list
+  // families.  A page p of a region starts at base + p * page_bytes; the allocator, the block tables and the prefix cache are
+  // the same for all of them.
+  struct PageRegion { char* base; size_t page_bytes; };
+  std::vector<PageRegion> regions;
+
+  // ---- layer-list families (Lerasun): fp32 residual stream, per-layer specs ----
+  std::vector<b2_layer_spec> specs;
+  std::vector<ListLayer> ll;
+  bool f32 = false;            // cfg.compute_f32
+  size_t esz = 2;              // bytes per operand element
+  int v_pad = 0;               // row stride of the bf16 logits the sampler reads (vocab rounded up to 8)
+  void *l_embed = nullptr, *l_head = nullptr;
+  float *l_embed_gain = nullptr, *l_final_gain = nullptr;
+  char* l_pool = nullptr;      // the latent cache
+  float *l_h = nullptr, *l_qd = nullptr, *l_qrot = nullptr, *l_qabs = nullptr, *l_mix = nullptr, *l_y = nullptr, *l_rw = nullptr,
+        *l_logits = nullptr;
+  void *l_x1 = nullptr, *l_x2 = nullptr, *l_qnope = nullptr, *l_olat = nullptr, *l_av = nullptr, *l_act = nullptr, *l_xl = nullptr;
+  int32_t *l_idx = nullptr, *l_offsets = nullptr, *l_slot_token = nullptr, *l_pair_slot = nullptr, *l_tile_group = nullptr,
+          *l_tile_row0 = nullptr, *l_ntiles = nullptr;
+  int l_max_top = 0, l_tiles_cap = 0, l_rows_cap = 0;
+  float* dbg_hidden_f32 = nullptr;
 };
 
 namespace {
@@ -800,6 +833,128 @@ int forward_layers(b2_engine* e, const Lane& ln, int T, int ntiles) {
   return 0;
 }
 
+// Layer-list families (Lerasun): h <- h + (mixer(n1(h)) + ff(n2(h))) on an fp32 residual stream.  The two norms of a
+// layer share one statistic (one kernel).  Mixer = latent attention in absorbed form (attn_latent.cu); feed-forward =
+// routed squared-ReLU experts as ragged groups of gemm_any.cu.  `rows` (device, nlast entries; null = every row) selects
+// the positions that get logits.  Operands are bf16, or fp32 when the engine was created with compute_f32.
+int forward_list(b2_engine* e, int T, int ntiles, int nlast) {
+  const b2_config& c = e->cfg;
+  const int W = c.hidden, f = e->f32 ? 1 : 0;
+  cudaStream_t st = e->stream;
+  auto dbg = [&](int slot) {
+    if ((e->debug_flags & 1) && e->dbg_hidden_f32 != nullptr && T <= e->dbg_cap_tokens)
+      cudaMemcpyAsync(e->dbg_hidden_f32 + (size_t)slot * e->dbg_cap_tokens * W, e->l_h, (size_t)T * W * 4, cudaMemcpyDeviceToDevice, st);
+  };
+  {
+    KL k(e, B2K_EMBED);
+    if (!k.skip()) B2_TRY(launch_embed_unit_norm(e->d_tokens, e->l_embed, f, e->l_embed_gain, e->l_h, T, W, c.vocab, c.rms_eps, st));
+  }
+  dbg(0);
+  const PrefillTile* tiles = ntiles > 0 ? e->d_tiles : nullptr;
+  for (int l = 0; l < c.num_layers; ++l) {
+    ListLayer& L = e->ll[l];
+    const b2_layer_spec& sp = L.sp;
+    const bool has_ff = sp.ff == B2_FF_ROUTED_EXPERTS;
+    const bool own = sp.kv_from < 0;
+    LatentGeom g{sp.heads, sp.dim, sp.rot_dim, sp.vdim, sp.kv_rank, sp.rot_dims, sp.rot_base, sp.scale, c.rms_eps};
+    char* cache_w = own ? e->regions[L.cache_region].base : nullptr;
+    const char* cache_r = e->regions[L.cache_region].base;
+    {
+      KL k(e, B2K_NORM);
+      if (!k.skip()) B2_TRY(launch_unit_norm2(e->l_h, L.gain1, has_ff ? L.gain2 : nullptr, e->l_x1, has_ff ? e->l_x2 : nullptr, f, T, W, c.rms_eps, nullptr, st));
+    }
+    {
+      KL k(e, B2K_GEMM_QKV);  // q of every head and, for a layer with its own latent, the latent and the shared key piece: one projection
+      AnyGemm a;
+      a.A = e->l_x1; a.W = L.wqd; a.C = e->l_qd; a.M = T; a.N = L.nqd; a.K = W; a.lda = W; a.ldw = W; a.ldc = L.nqd;
+      if (!k.skip()) B2_TRY(launch_gemm_any(a, f, f, 1, 1, 0, st));
+    }
+    {
+      KL k(e, B2K_ROPE_KV);
+      if (!k.skip()) B2_TRY(launch_latent_finish(e->l_qd, L.nqd, g, own ? 1 : 0, L.lat_gain, e->d_positions, e->d_slots, e->l_qnope, f, e->l_qrot, cache_w, f, T, st));
+    }
+    {
+      KL k(e, B2K_GEMM_QKV);  // the query pulled through the key up-projection, all heads in one strided batch
+      AnyGemm a;
+      a.A = e->l_qnope; a.W = L.ukT; a.C = e->l_qabs; a.M = T; a.N = sp.kv_rank; a.K = sp.dim;
+      a.lda = (long)sp.heads * sp.dim; a.ldw = sp.dim; a.ldc = (long)sp.heads * sp.kv_rank;
+      a.a_bs = sp.dim; a.w_bs = (long)sp.kv_rank * sp.dim; a.c_bs = sp.kv_rank;
+      if (!k.skip()) B2_TRY(launch_gemm_any(a, f, f, 1, sp.heads, 0, st));
+    }
+    {
+      KL k(e, ntiles > 0 ? B2K_MISC : B2K_ATTN_DECODE);
+      if (!k.skip()) B2_TRY(launch_latent_attention(e->l_qabs, e->l_qrot, cache_r, f, g, e->d_block_table, e->bt_stride, c.block_size, tiles, ntiles,
+                                                    e->d_positions, e->d_seq_lens, L.sink, e->l_olat, f, T, st));
+    }
+    {
+      KL k(e, B2K_GEMM_O);  // values of every head from the weighted latent
+      AnyGemm a;
+      a.A = e->l_olat; a.W = L.uv; a.C = e->l_av; a.M = T; a.N = sp.vdim; a.K = sp.kv_rank;
+      a.lda = (long)sp.heads * sp.kv_rank; a.ldw = sp.kv_rank; a.ldc = (long)sp.heads * sp.vdim;
+      a.a_bs = sp.kv_rank; a.w_bs = (long)sp.vdim * sp.kv_rank; a.c_bs = sp.vdim;
+      if (!k.skip()) B2_TRY(launch_gemm_any(a, f, f, f, sp.heads, 0, st));
+    }
+    {
+      KL k(e, B2K_GEMM_O);
+      AnyGemm a;
+      a.A = e->l_av; a.W = L.wo; a.C = e->l_mix; a.M = T; a.N = W; a.K = sp.heads * sp.vdim; a.lda = a.K; a.ldw = a.K; a.ldc = W;
+      if (!k.skip()) B2_TRY(launch_gemm_any(a, f, f, 1, 1, 0, st));
+    }
+    if (has_ff) {
+      RouteGeom rg{sp.experts, sp.top, sp.groups, sp.groups_keep};
+      {
+        KL k(e, B2K_ACT);
+        if (!k.skip()) B2_TRY(launch_route(e->l_x2, f, L.router, L.corr, rg, e->l_idx, e->l_rw, T, W, st));
+      }
+      {
+        KL k(e, B2K_MISC);
+        if (!k.skip()) B2_TRY(launch_route_permute(e->l_idx, T, sp.top, sp.experts, e->l_offsets, e->l_slot_token, e->l_pair_slot, st));
+      }
+      const int max_tiles = std::min(e->l_tiles_cap, (T * sp.top + any_gemm_tile_rows() - 1) / any_gemm_tile_rows() + sp.experts);
+      {
+        KL k(e, B2K_MISC);
+        if (!k.skip()) B2_TRY(launch_ragged_tiles(e->l_offsets, sp.experts, e->l_tile_group, e->l_tile_row0, e->l_ntiles, max_tiles, st));
+      }
+      AnyGemm a;
+      a.tile_group = e->l_tile_group; a.tile_row0 = e->l_tile_row0; a.n_tiles = e->l_ntiles; a.group_offsets = e->l_offsets;
+      {
+        KL k(e, B2K_GEMM_GATEUP);  // act[slot] = relu(U_e x[token(slot)])^2
+        a.A = e->l_x2; a.a_rows = e->l_slot_token; a.W = L.up; a.C = e->l_act; a.N = sp.ff_dim; a.K = W; a.lda = W; a.ldw = W; a.ldc = sp.ff_dim;
+        a.w_bs = (long)sp.ff_dim * W; a.epilogue = ANY_EPI_RELU2;
+        if (!k.skip()) B2_TRY(launch_gemm_any(a, f, f, f, 1, max_tiles, st));
+      }
+      {
+        KL k(e, B2K_GEMM_DOWN);  // y[slot] = D_e act[slot]
+        a.A = e->l_act; a.a_rows = nullptr; a.W = L.down; a.C = e->l_y; a.N = W; a.K = sp.ff_dim; a.lda = sp.ff_dim; a.ldw = sp.ff_dim; a.ldc = W;
+        a.w_bs = (long)W * sp.ff_dim; a.epilogue = ANY_EPI_STORE;
+        if (!k.skip()) B2_TRY(launch_gemm_any(a, f, f, 1, 1, max_tiles, st));
+      }
+    }
+    {
+      KL k(e, B2K_NORM);  // h += mixer + sum_k w_k y_k
+      if (!k.skip()) B2_TRY(launch_route_combine(e->l_h, e->l_mix, e->l_y, e->l_rw, e->l_pair_slot, T, W, has_ff ? sp.top : 0, st));
+    }
+    dbg(l + 1);
+  }
+  {
+    KL k(e, B2K_NORM);
+    if (!k.skip()) B2_TRY(launch_unit_norm2(e->l_h, e->l_final_gain, nullptr, e->l_xl, nullptr, f, nlast, W, c.rms_eps, ntiles > 0 ? e->d_last_rows : nullptr, st));
+  }
+  {
+    KL k(e, B2K_LMHEAD);
+    AnyGemm a;
+    a.A = e->l_xl; a.W = e->l_head; a.C = e->l_logits; a.M = nlast; a.N = c.vocab; a.K = W; a.lda = W; a.ldw = W; a.ldc = c.vocab;
+    a.alpha = c.logit_scale != 0.f ? c.logit_scale : 1.f;
+    if (!k.skip()) B2_TRY(launch_gemm_any(a, f, f, 1, 1, 0, st));
+  }
+  {
+    KL k(e, B2K_MISC);
+    bf16* lb = (e->debug_flags & 2) ? e->logits : nullptr;  // the sampler's rows: one per sequence, the leading rows
+    if (!k.skip()) B2_TRY(launch_logits_finish(e->l_logits, e->d_out_tokens, lb, bucket_batch(std::max(c.max_seqs, 1)), nlast, c.vocab, e->v_pad, st));
+  }
+  return 0;
+}
+
 // Two-lane decode.  At batch 64 a decode step is two things that do not overlap when they depend on each other: the
 // attention pass of a layer (HBM-bound, about half the step) and the eight small kernels between two attention
 // passes (a chain of dependent launches that moves 31 MB of weights in ~30 us: latency-bound, HBM nearly idle).
@@ -818,6 +973,7 @@ int forward(b2_engine* e, int T, int ntiles, int nlast, int attn_split) {
   const b2_config& c = e->cfg;
   const int H = c.hidden;
   (void)attn_split;
+  if (c.arch == B2_ARCH_LERASUN) return forward_list(e, T, ntiles, nlast);
   if (c.arch == B2_ARCH_OPT) return forward_opt(e, T, ntiles, nlast);
   if (ntiles == 0 && e->use_chain == 2 && e->fused_ok && c.arch == B2_ARCH_QWEN3 && !(e->debug_flags & 1) &&
       e->force_gemm_impl != 0 && T > e->simt_max_tokens && T <= 64 && e->skip_mask == 0)
@@ -1145,11 +1301,219 @@ int ensure_logits(b2_engine* e) {
   if (e->logits) return 0;
   // rows for the padded graph bucket: a captured step runs the lm_head over bucket_batch(n) rows, and max_seqs need
   // not be a bucket value (--max-num-seqs is free-form)
-  return dalloc(&e->logits, (size_t)bucket_batch(std::max(e->cfg.max_seqs, 1)) * e->cfg.vocab);
+  return dalloc(&e->logits, (size_t)bucket_batch(std::max(e->cfg.max_seqs, 1)) * (e->v_pad > 0 ? e->v_pad : e->cfg.vocab));
+}
+
+// ---- layer-list families: tensors by name ----
+// Uploads n bf16 values as operand elements (bf16 as they are, or widened to fp32 -- exact) at element offset `off` of dst.
+int put_operand(b2_engine* e, void* dst, size_t off, const uint16_t* src, size_t n) {
+  if (!e->f32) {
+    B2_CUDA_OK(cudaMemcpy(reinterpret_cast<uint16_t*>(dst) + off, src, n * 2, cudaMemcpyHostToDevice));
+    return 0;
+  }
+  std::vector<uint32_t> wide(n);
+  for (size_t i = 0; i < n; ++i) wide[i] = (uint32_t)src[i] << 16;
+  B2_CUDA_OK(cudaMemcpy(reinterpret_cast<uint32_t*>(dst) + off, wide.data(), n * 4, cudaMemcpyHostToDevice));
+  return 0;
+}
+// fp32 copy of n bf16 values, plus `add` (a gain stored around zero becomes 1 + g)
+int put_f32(float* dst, const uint16_t* src, size_t n, float add) {
+  std::vector<float> v(n);
+  for (size_t i = 0; i < n; ++i) {
+    const uint32_t u = (uint32_t)src[i] << 16;
+    float f;
+    memcpy(&f, &u, 4);
+    v[i] = f + add;
+  }
+  B2_CUDA_OK(cudaMemcpy(dst, v.data(), n * 4, cudaMemcpyHostToDevice));
+  return 0;
+}
+
+int list_tensor(b2_engine* e, const std::string& name, const void* host, size_t nbytes) {
+  const b2_config& c = e->cfg;
+  const size_t W = c.hidden;
+  const uint16_t* src = reinterpret_cast<const uint16_t*>(host);
+  auto want = [&](size_t elems) -> int {
+    if (nbytes != elems * 2) {
+      b2_set_error("tensor %s: expected %zu bytes, got %zu", name.c_str(), elems * 2, nbytes);
+      return -22;
+    }
+    return 0;
+  };
+  auto done = [&](int rc) {
+    if (rc == 0) e->loaded[name] = 1;
+    return rc;
+  };
+  if (name == "embed") { B2_TRY(want((size_t)c.vocab * W)); return done(put_operand(e, e->l_embed, 0, src, (size_t)c.vocab * W)); }
+  if (name == "head") { B2_TRY(want((size_t)c.vocab * W)); return done(put_operand(e, e->l_head, 0, src, (size_t)c.vocab * W)); }
+  if (name == "embed.norm") { B2_TRY(want(W)); return done(put_f32(e->l_embed_gain, src, W, 1.0f)); }
+  if (name == "final.norm") { B2_TRY(want(W)); return done(put_f32(e->l_final_gain, src, W, 1.0f)); }
+  size_t dot = name.find('.');
+  if (name.size() < 3 || name[0] != 'l' || dot == std::string::npos || dot < 2) {
+    b2_set_error("unknown tensor name %s", name.c_str());
+    return -22;
+  }
+  const int li = atoi(name.substr(1, dot - 1).c_str());
+  if (li < 0 || li >= c.num_layers) {
+    b2_set_error("tensor %s: layer out of range", name.c_str());
+    return -22;
+  }
+  ListLayer& L = e->ll[li];
+  const b2_layer_spec& sp = L.sp;
+  const std::string rest = name.substr(dot + 1);
+  const size_t H = sp.heads, dn = sp.dim, dr = sp.rot_dim, dv = sp.vdim, r = sp.kv_rank, ff = sp.ff_dim;
+  if (rest == "norm1") { B2_TRY(want(W)); return done(put_f32(L.gain1, src, W, 1.0f)); }
+  if (rest == "norm2" && L.gain2) { B2_TRY(want(W)); return done(put_f32(L.gain2, src, W, 1.0f)); }
+  if (rest == "mix.q") { B2_TRY(want((size_t)L.nq * W)); return done(put_operand(e, L.wqd, 0, src, (size_t)L.nq * W)); }
+  if (rest == "mix.dkv" && sp.kv_from < 0) { B2_TRY(want((r + dr) * W)); return done(put_operand(e, L.wqd, (size_t)L.nq * W, src, (r + dr) * W)); }
+  if (rest == "mix.dkv.norm" && sp.kv_from < 0) { B2_TRY(want(r)); return done(put_f32(L.lat_gain, src, r, 0.0f)); }
+  if (rest == "mix.uk") {  // stored [heads * dim][kv_rank]; kept per head as [kv_rank][dim], the layout the absorbed-query product reads
+    B2_TRY(want(H * dn * r));
+    std::vector<uint16_t> tr(H * dn * r);
+    for (size_t a = 0; a < H; ++a)
+      for (size_t d = 0; d < dn; ++d)
+        for (size_t j = 0; j < r; ++j) tr[(a * r + j) * dn + d] = src[(a * dn + d) * r + j];
+    return done(put_operand(e, L.ukT, 0, tr.data(), tr.size()));
+  }
+  if (rest == "mix.uv") { B2_TRY(want(H * dv * r)); return done(put_operand(e, L.uv, 0, src, H * dv * r)); }
+  if (rest == "mix.sink") { B2_TRY(want(H)); return done(put_f32(L.sink, src, H, 0.0f)); }
+  if (rest == "mix.o") { B2_TRY(want(W * H * dv)); return done(put_operand(e, L.wo, 0, src, W * H * dv)); }
+  if (sp.ff == B2_FF_ROUTED_EXPERTS) {
+    if (rest == "mlp.router") { B2_TRY(want((size_t)sp.experts * W)); return done(put_f32(L.router, src, (size_t)sp.experts * W, 0.0f)); }
+    if (rest == "mlp.correction") { B2_TRY(want((size_t)sp.experts)); return done(put_f32(L.corr, src, (size_t)sp.experts, 0.0f)); }
+    if (rest.compare(0, 5, "mlp.e") == 0) {
+      size_t d2 = rest.find('.', 5);
+      if (d2 != std::string::npos) {
+        const int ex = atoi(rest.substr(5, d2 - 5).c_str());
+        const std::string which = rest.substr(d2 + 1);
+        if (ex >= 0 && ex < sp.experts && which == "up") { B2_TRY(want(ff * W)); return done(put_operand(e, L.up, (size_t)ex * ff * W, src, ff * W)); }
+        if (ex >= 0 && ex < sp.experts && which == "down") { B2_TRY(want(W * ff)); return done(put_operand(e, L.down, (size_t)ex * W * ff, src, W * ff)); }
+      }
+    }
+  }
+  b2_set_error("unknown tensor name %s", name.c_str());
+  return -22;
+}
+
+int list_tensor_count(const b2_engine* e) {
+  int n = 4;
+  for (const ListLayer& L : e->ll) {
+    n += 1 + 5 + (L.sp.kv_from < 0 ? 2 : 0);  // norm1; q, uk, uv, sink, o; dkv, dkv.norm
+    if (L.sp.ff == B2_FF_ROUTED_EXPERTS) n += 1 + 2 + 2 * L.sp.experts;  // norm2; router, correction; experts
+  }
+  return n;
+}
+
+// Validates the layer list and allocates weights, activations and scratch of a layer-list engine.
+int list_engine_alloc(b2_engine* e) {
+  const b2_config& c = e->cfg;
+  const size_t W = c.hidden, es = e->esz;
+  B2_REQUIRE(!e->specs.empty() && (int)e->specs.size() == c.num_layers, "Lerasun: layer_specs missing");
+  B2_REQUIRE(c.hidden >= 1 && c.vocab >= 1 && c.num_layers >= 1, "Lerasun: bad sizes");
+  auto xalloc = [&](void** p, size_t elems) -> int {
+    char* q = nullptr;
+    B2_TRY(dalloc(&q, std::max<size_t>(elems, 1) * es));
+    *p = q;
+    e->weight_bytes += (int64_t)(elems * es);
+    return 0;
+  };
+  auto falloc = [&](float** p, size_t n) -> int {
+    B2_TRY(dalloc(p, std::max<size_t>(n, 1)));
+    e->weight_bytes += (int64_t)(n * 4);
+    return 0;
+  };
+  e->weight_bytes = 0;
+  B2_TRY(xalloc(&e->l_embed, (size_t)c.vocab * W));
+  B2_TRY(xalloc(&e->l_head, (size_t)c.vocab * W));
+  B2_TRY(falloc(&e->l_embed_gain, W));
+  B2_TRY(falloc(&e->l_final_gain, W));
+  e->ll.resize(c.num_layers);
+  size_t max_nqd = 1, max_hn = 1, max_hr = 1, max_hrot = 1, max_hv = 1, max_ff = 1;
+  int max_top = 1, max_exp = 1;
+  for (int l = 0; l < c.num_layers; ++l) {
+    ListLayer& L = e->ll[l];
+    L.sp = e->specs[l];
+    const b2_layer_spec& sp = L.sp;
+    B2_REQUIRE(sp.mixer == B2_MIXER_LATENT_ATTENTION, "layer %d: mixer kind %d not built", l, sp.mixer);
+    B2_REQUIRE(sp.heads >= 1 && sp.dim >= 1 && sp.rot_dim >= 0 && sp.vdim >= 1 && sp.kv_rank >= 1, "layer %d: bad mixer sizes", l);
+    B2_REQUIRE(sp.rot_dims >= 0 && sp.rot_dims <= sp.rot_dim && sp.rot_dims % 2 == 0, "layer %d: rot dims %d must be even and <= rot_dim %d", l, sp.rot_dims, sp.rot_dim);
+    if (sp.kv_from >= 0) {
+      B2_REQUIRE(sp.kv_from < l && e->specs[sp.kv_from].kv_from < 0, "layer %d: kv_from %d must name an earlier layer with its own latent", l, sp.kv_from);
+      const b2_layer_spec& o = e->specs[sp.kv_from];
+      B2_REQUIRE(o.kv_rank == sp.kv_rank && o.rot_dim == sp.rot_dim, "layer %d: latent sizes differ from layer %d's", l, sp.kv_from);
+    }
+    B2_REQUIRE(sp.ff == B2_FF_NONE || sp.ff == B2_FF_ROUTED_EXPERTS, "layer %d: feed-forward kind %d not built", l, sp.ff);
+    L.nq = sp.heads * (sp.dim + sp.rot_dim);
+    L.nqd = L.nq + (sp.kv_from < 0 ? sp.kv_rank + sp.rot_dim : 0);
+    B2_TRY(xalloc(&L.wqd, (size_t)L.nqd * W));
+    B2_TRY(xalloc(&L.ukT, (size_t)sp.heads * sp.kv_rank * sp.dim));
+    B2_TRY(xalloc(&L.uv, (size_t)sp.heads * sp.vdim * sp.kv_rank));
+    B2_TRY(xalloc(&L.wo, W * sp.heads * sp.vdim));
+    B2_TRY(falloc(&L.gain1, W));
+    B2_TRY(falloc(&L.sink, sp.heads));
+    if (sp.kv_from < 0) B2_TRY(falloc(&L.lat_gain, sp.kv_rank));
+    if (sp.ff == B2_FF_ROUTED_EXPERTS) {
+      B2_REQUIRE(sp.experts >= 1 && sp.top >= 1 && sp.ff_dim >= 1 && sp.groups >= 1 && sp.experts % sp.groups == 0 && sp.groups_keep >= 1 &&
+                     sp.groups_keep <= sp.groups && sp.top <= sp.groups_keep * (sp.experts / sp.groups),
+                 "layer %d: bad router sizes (experts %d, top %d, groups %d, keep %d)", l, sp.experts, sp.top, sp.groups, sp.groups_keep);
+      B2_TRY(falloc(&L.gain2, W));
+      B2_TRY(falloc(&L.router, (size_t)sp.experts * W));
+      B2_TRY(falloc(&L.corr, sp.experts));
+      B2_TRY(xalloc(&L.up, (size_t)sp.experts * sp.ff_dim * W));
+      B2_TRY(xalloc(&L.down, (size_t)sp.experts * W * sp.ff_dim));
+      max_top = std::max(max_top, sp.top);
+      max_exp = std::max(max_exp, sp.experts);
+      max_ff = std::max(max_ff, (size_t)sp.ff_dim);
+    }
+    max_nqd = std::max(max_nqd, (size_t)L.nqd);
+    max_hn = std::max(max_hn, (size_t)sp.heads * sp.dim);
+    max_hr = std::max(max_hr, (size_t)sp.heads * sp.kv_rank);
+    max_hrot = std::max(max_hrot, (size_t)sp.heads * std::max(sp.rot_dim, 1));
+    max_hv = std::max(max_hv, (size_t)sp.heads * sp.vdim);
+  }
+  // ---- activations ----
+  e->cap_tokens = ((std::max(c.max_batch_tokens, c.max_seqs) + 255) / 256) * 256;
+  const size_t Tc = e->cap_tokens;
+  e->l_rows_cap = (int)(Tc + bucket_batch(c.max_seqs));
+  e->l_max_top = max_top;
+  e->v_pad = (c.vocab + 7) / 8 * 8;
+  auto aalloc = [&](void** p, size_t elems) -> int {
+    char* q = nullptr;
+    B2_TRY(dalloc(&q, elems * es));
+    *p = q;
+    return 0;
+  };
+  B2_TRY(dalloc(&e->l_h, Tc * W));
+  B2_TRY(dalloc(&e->l_qd, Tc * max_nqd));
+  B2_TRY(dalloc(&e->l_qrot, Tc * max_hrot));
+  B2_TRY(dalloc(&e->l_qabs, Tc * max_hr));
+  B2_TRY(dalloc(&e->l_mix, Tc * W));
+  B2_TRY(dalloc(&e->l_y, Tc * max_top * W));
+  B2_TRY(dalloc(&e->l_rw, Tc * max_top));
+  B2_TRY(dalloc(&e->l_logits, (size_t)e->l_rows_cap * c.vocab));
+  B2_TRY(aalloc(&e->l_x1, Tc * W));
+  B2_TRY(aalloc(&e->l_x2, Tc * W));
+  B2_TRY(aalloc(&e->l_qnope, Tc * max_hn));
+  B2_TRY(aalloc(&e->l_olat, Tc * max_hr));
+  B2_TRY(aalloc(&e->l_av, Tc * max_hv));
+  B2_TRY(aalloc(&e->l_act, Tc * max_top * max_ff));
+  B2_TRY(aalloc(&e->l_xl, (size_t)e->l_rows_cap * W));
+  B2_TRY(dalloc(&e->l_idx, Tc * max_top));
+  B2_TRY(dalloc(&e->l_offsets, (size_t)max_exp + 1));
+  B2_TRY(dalloc(&e->l_slot_token, Tc * max_top));
+  B2_TRY(dalloc(&e->l_pair_slot, Tc * max_top));
+  e->l_tiles_cap = (int)(Tc * max_top / any_gemm_tile_rows() + max_exp + 1);
+  B2_TRY(dalloc(&e->l_tile_group, (size_t)e->l_tiles_cap));
+  B2_TRY(dalloc(&e->l_tile_row0, (size_t)e->l_tiles_cap));
+  B2_TRY(dalloc(&e->l_ntiles, (size_t)1));
+  B2_CUDA_OK(cudaMemset(e->l_ntiles, 0, 4));
+  B2_CUDA_OK(cudaMemset(e->l_pair_slot, 0, Tc * max_top * 4));
+  return 0;
 }
 
 int layer_tensor(b2_engine* e, const std::string& name, const void* host, size_t nbytes) {
   const b2_config& c = e->cfg;
+  if (c.arch == B2_ARCH_LERASUN) return list_tensor(e, name, host, nbytes);
   const int H = c.hidden, I = c.intermediate;
   auto put = [&](bf16* dst, size_t elems) -> int {
     if (nbytes != elems * 2) {
@@ -1402,23 +1766,26 @@ int load_safetensors(b2_engine* e, const char* path) {
 extern "C" int b2_engine_create(const b2_config* cfg, const char* safetensors_path, int device, b2_engine** out) {
   B2_REQUIRE(cfg != nullptr && out != nullptr, "b2_engine_create: null argument");
   B2_REQUIRE(cfg->abi_version == B2_ABI_VERSION, "b2_engine_create: abi_version %d != %d", cfg->abi_version, B2_ABI_VERSION);
-  B2_REQUIRE(cfg->arch == B2_ARCH_QWEN3 || cfg->arch == B2_ARCH_PHI3 || cfg->arch == B2_ARCH_OPT,
-             "arch %d not built (0 = Qwen3, 1 = Phi-3, 2 = OPT)", cfg->arch);
+  B2_REQUIRE(cfg->arch == B2_ARCH_QWEN3 || cfg->arch == B2_ARCH_PHI3 || cfg->arch == B2_ARCH_OPT || cfg->arch == B2_ARCH_LERASUN,
+             "arch %d not built (0 = Qwen3, 1 = Phi-3, 2 = OPT, 3 = Lerasun)", cfg->arch);
+  const bool ls = cfg->arch == B2_ARCH_LERASUN;  // a layer-list family: its sizes live in layer_specs and are checked in list_engine_alloc
+  B2_REQUIRE(ls || !cfg->compute_f32, "compute_f32: only the Lerasun family has an fp32 path");
+  B2_REQUIRE(!ls || cfg->layer_specs != nullptr, "Lerasun: layer_specs is NULL");
   B2_REQUIRE(cfg->arch != B2_ARCH_OPT || cfg->tie_embeddings, "OPT: the lm_head is tied to embed_tokens");
   B2_REQUIRE(cfg->sliding_window >= 0 && (cfg->sliding_window == 0 || cfg->arch == B2_ARCH_PHI3),
              "sliding_window %d: only the Phi-3 family has one", cfg->sliding_window);
-  B2_REQUIRE(cfg->head_dim >= 8 && cfg->head_dim <= 128 && cfg->head_dim % 8 == 0, "head_dim %d not supported (multiple of 8, <= 128)",
+  B2_REQUIRE(ls || (cfg->head_dim >= 8 && cfg->head_dim <= 128 && cfg->head_dim % 8 == 0), "head_dim %d not supported (multiple of 8, <= 128)",
              cfg->head_dim);
-  B2_REQUIRE(cfg->num_kv_heads >= 1 && (cfg->num_q_heads == 2 * cfg->num_kv_heads || cfg->num_q_heads == cfg->num_kv_heads),
+  B2_REQUIRE(ls || (cfg->num_kv_heads >= 1 && (cfg->num_q_heads == 2 * cfg->num_kv_heads || cfg->num_q_heads == cfg->num_kv_heads)),
              "query heads per kv head must be 1 or 2 (nq=%d nkv=%d)", cfg->num_q_heads, cfg->num_kv_heads);
-  {
+  if (!ls) {
     const int rd = cfg->arch == B2_ARCH_OPT ? 0 : (cfg->rotary_dim > 0 ? cfg->rotary_dim : cfg->head_dim);
     B2_REQUIRE(rd % 8 == 0 && rd <= cfg->head_dim, "rotary_dim %d must be a multiple of 8 and <= head_dim", rd);
     B2_REQUIRE(cfg->arch != B2_ARCH_QWEN3 || (rd == cfg->head_dim && cfg->head_dim == 128),
                "Qwen3: QK-norm is built for 128-wide, fully rotated heads (head_dim %d, rotary_dim %d)", cfg->head_dim, rd);
   }
   B2_REQUIRE(cfg->block_size == 16, "block_size %d not built (16 only)", cfg->block_size);
-  B2_REQUIRE(cfg->hidden % 256 == 0 && cfg->intermediate % 256 == 0, "hidden/intermediate must be multiples of 256");
+  B2_REQUIRE(ls || (cfg->hidden % 256 == 0 && cfg->intermediate % 256 == 0), "hidden/intermediate must be multiples of 256");
   B2_REQUIRE(cfg->max_seqs >= 1 && cfg->max_batch_tokens >= 1 && cfg->max_model_len >= 1, "bad sizing");
   int ndev = 0;
   cudaError_t ce = cudaGetDeviceCount(&ndev);
@@ -1435,6 +1802,14 @@ extern "C" int b2_engine_create(const b2_config* cfg, const char* safetensors_pa
   b2_engine* e = new b2_engine();
   e->cfg = *cfg;
   e->cfg.rope_inv_freq = nullptr;
+  e->cfg.layer_specs = nullptr;
+  if (ls) {
+    e->specs.assign(cfg->layer_specs, cfg->layer_specs + cfg->num_layers);
+    e->f32 = cfg->compute_f32 != 0;
+    e->esz = e->f32 ? 4 : 2;
+    e->cfg.num_kv_heads = e->cfg.num_q_heads = 1;  // unused by this family; keeps the derived GQA geometry below finite
+    e->cfg.head_dim = 128;
+  }
   e->device = device;
   e->num_sms = prop.multiProcessorCount;
   const b2_config& c = e->cfg;
@@ -1487,6 +1862,8 @@ extern "C" int b2_engine_create(const b2_config* cfg, const char* safetensors_pa
   } while (0)
   {
     E_CUDA(cudaStreamCreateWithFlags(&e->stream, cudaStreamNonBlocking));
+    if (ls) E_TRY(list_engine_alloc(e));
+    if (!ls) {
     // ---- weights ----
     E_TRY(dalloc(&e->embed, (size_t)c.vocab * H));
     if (c.tie_embeddings) e->lm_head = e->embed;
@@ -1609,6 +1986,8 @@ extern "C" int b2_engine_create(const b2_config* cfg, const char* safetensors_pa
       E_TRY(b2_make_tmap_bf16(&L.tm_d, L.wd, H, I, I, 128));
     }
     E_TRY(b2_make_tmap_bf16(&e->tm_lm_head, e->lm_head, c.vocab, H, H, 128));
+    }  // !ls
+    const size_t Tc = e->cap_tokens;
     // ---- batch state ----
     e->bt_stride = (c.max_model_len + c.block_size - 1) / c.block_size;
     const size_t Bcap = bucket_batch(c.max_seqs);
@@ -1617,8 +1996,8 @@ extern "C" int b2_engine_create(const b2_config* cfg, const char* safetensors_pa
     E_TRY(dalloc(&e->d_slots, Tc));
     E_TRY(dalloc(&e->d_seq_lens, Bcap));
     E_TRY(dalloc(&e->d_block_table, Bcap * e->bt_stride));
-    E_TRY(dalloc(&e->d_last_rows, Bcap));
-    E_TRY(dalloc(&e->d_out_tokens, Bcap));
+    E_TRY(dalloc(&e->d_last_rows, Bcap + (ls ? Tc : 0)));  // layer-list families: logits at any of a call's rows
+    E_TRY(dalloc(&e->d_out_tokens, Bcap + (ls ? Tc : 0)));
     E_TRY(dalloc(&e->d_argmax, Bcap));
     E_TRY(dalloc(&e->d_step, (size_t)1));
     E_TRY(dalloc(&e->d_pf_frac, (size_t)1));
@@ -1629,7 +2008,7 @@ extern "C" int b2_engine_create(const b2_config* cfg, const char* safetensors_pa
     E_TRY(dalloc(&e->d_gbar2, (size_t)1));
     E_CUDA(cudaMemset(e->d_gbar2, 0, 8));
     // the fused chain spins on a grid-wide barrier: all of its 32 clusters must be resident at once
-    e->fused_ok = e->native_geom && c.arch == B2_ARCH_QWEN3 &&
+    e->fused_ok = !ls && e->native_geom && c.arch == B2_ARCH_QWEN3 &&
                   fused_chain_supported(H, I, e->nq, e->nkv, e->hd, 1, c.block_size) && fused_chain_max_clusters() >= 32;
     E_TRY(dalloc(&e->d_ss, (size_t)2 * 32 * 64));
     E_CUDA(cudaMemset(e->d_ss, 0, 2 * 32 * 64 * 4));
@@ -1640,7 +2019,7 @@ extern "C" int b2_engine_create(const b2_config* cfg, const char* safetensors_pa
     E_CUDA(cudaMemset(e->d_block_table, 0, Bcap * e->bt_stride * 4));
     e->tiles_cap = (int)(Tc / 64 + 2 * Bcap + 16);
     E_TRY(dalloc(&e->d_tiles, (size_t)e->tiles_cap));
-    e->h_stage_ints = std::max((size_t)3 * Tc + Bcap * (size_t)e->bt_stride + 4 * Bcap, (size_t)1 << 16);
+    e->h_stage_ints = std::max((size_t)4 * Tc + Bcap * (size_t)e->bt_stride + 5 * Bcap, (size_t)1 << 16);
     E_CUDA(cudaMallocHost(&e->h_stage, e->h_stage_ints * sizeof(int32_t)));
     E_CUDA(cudaMallocHost(&e->h_tiles, (size_t)e->tiles_cap * sizeof(PrefillTile)));
     E_CUDA(cudaMallocHost(&e->h_out, (size_t)e->log_cap_steps * c.max_seqs * sizeof(int32_t)));
@@ -1650,13 +2029,20 @@ extern "C" int b2_engine_create(const b2_config* cfg, const char* safetensors_pa
     // ---- KV pool ----
     {
       const size_t blk_elems = (size_t)e->nkv * c.block_size * e->hd;
+      // bytes one page takes in all regions together
+      size_t page_bytes_all = blk_elems * 2 * 2 * c.num_layers;
+      if (ls) {
+        page_bytes_all = 0;
+        for (const ListLayer& L : e->ll)
+          if (L.sp.kv_from < 0) page_bytes_all += (size_t)c.block_size * (L.sp.kv_rank + L.sp.rot_dim) * e->esz;
+      }
       int64_t nb = c.num_blocks;
       if (nb <= 0) {
         size_t free_b = 0, total_b = 0;
         E_CUDA(cudaMemGetInfo(&free_b, &total_b));
         const double frac = c.gpu_mem_fraction > 0 ? c.gpu_mem_fraction : 0.9;
         const double usable = (double)free_b - (1.0 - frac) * (double)total_b - (512.0 * 1024 * 1024);
-        nb = (int64_t)(usable / ((double)blk_elems * 2 * 2 * c.num_layers));
+        nb = (int64_t)(usable / (double)page_bytes_all);
         if (nb < 16) {
           b2_set_error("not enough free device memory for a KV pool (free %zu MiB)", free_b >> 20);
           rc = -12;
@@ -1665,8 +2051,25 @@ extern "C" int b2_engine_create(const b2_config* cfg, const char* safetensors_pa
       }
       e->num_blocks = nb;
       e->layer_kv_elems = (size_t)nb * blk_elems;
-      E_TRY(dalloc(&e->kv_pool, (size_t)2 * c.num_layers * e->layer_kv_elems));
-      E_CUDA(cudaMemset(e->kv_pool, 0, (size_t)2 * c.num_layers * e->layer_kv_elems * 2));
+      if (ls) {
+        E_TRY(dalloc(&e->l_pool, (size_t)nb * page_bytes_all));
+        E_CUDA(cudaMemset(e->l_pool, 0, (size_t)nb * page_bytes_all));
+        size_t off = 0;
+        for (ListLayer& L : e->ll) {
+          if (L.sp.kv_from >= 0) continue;
+          const size_t pb = (size_t)c.block_size * (L.sp.kv_rank + L.sp.rot_dim) * e->esz;
+          L.cache_region = (int)e->regions.size();
+          e->regions.push_back({e->l_pool + off, pb});
+          off += (size_t)nb * pb;
+        }
+        for (ListLayer& L : e->ll)
+          if (L.sp.kv_from >= 0) L.cache_region = e->ll[L.sp.kv_from].cache_region;
+      } else {
+        E_TRY(dalloc(&e->kv_pool, (size_t)2 * c.num_layers * e->layer_kv_elems));
+        E_CUDA(cudaMemset(e->kv_pool, 0, (size_t)2 * c.num_layers * e->layer_kv_elems * 2));
+        for (int r = 0; r < 2 * c.num_layers; ++r)
+          e->regions.push_back({reinterpret_cast<char*>(e->kv_pool + (size_t)r * e->layer_kv_elems), blk_elems * 2});
+      }
       e->free_blocks.reserve(nb);
       for (int64_t b = nb - 1; b >= 1; --b) e->free_blocks.push_back((int32_t)b);  // page 0 = null page
       e->blk_ref.assign(nb, 0);
@@ -1709,6 +2112,12 @@ extern "C" int b2_engine_load_safetensors(b2_engine* e, const char* path) {
 extern "C" int b2_engine_finalize(b2_engine* e) {
   B2_REQUIRE(e, "b2_engine_finalize: null engine");
   const int arch = e->cfg.arch;
+  if (arch == B2_ARCH_LERASUN) {
+    const int want = list_tensor_count(e);
+    B2_REQUIRE((int)e->loaded.size() == want, "weights incomplete: %d of %d tensors loaded", (int)e->loaded.size(), want);
+    e->finalized = true;
+    return 0;
+  }
   const int per_layer = arch == B2_ARCH_QWEN3 ? 11 : arch == B2_ARCH_PHI3 ? 6 : 16;
   const int want = (arch == B2_ARCH_OPT ? 4 : 2) + e->cfg.num_layers * per_layer;
   int have = 0;
@@ -1748,6 +2157,12 @@ extern "C" void b2_engine_free(b2_engine* e) {
   if (e->h_tok) cudaFreeHost(e->h_tok);
   if (e->ev_tok) cudaEventDestroy(e->ev_tok);
   F(e->partial2); F(e->attn_scratch2); F(e->ssq);
+  F(e->l_embed); F(e->l_head); F(e->l_embed_gain); F(e->l_final_gain); F(e->l_pool); F(e->l_h); F(e->l_qd); F(e->l_qrot); F(e->l_qabs);
+  F(e->l_mix); F(e->l_y); F(e->l_rw); F(e->l_logits); F(e->l_x1); F(e->l_x2); F(e->l_qnope); F(e->l_olat); F(e->l_av); F(e->l_act); F(e->l_xl);
+  F(e->l_idx); F(e->l_offsets); F(e->l_slot_token); F(e->l_pair_slot); F(e->l_tile_group); F(e->l_tile_row0); F(e->l_ntiles); F(e->dbg_hidden_f32);
+  for (auto& L : e->ll) {
+    F(L.wqd); F(L.ukT); F(L.uv); F(L.wo); F(L.up); F(L.down); F(L.gain1); F(L.gain2); F(L.lat_gain); F(L.sink); F(L.router); F(L.corr);
+  }
   if (e->ev_fork) cudaEventDestroy(e->ev_fork);
   if (e->ev_join) cudaEventDestroy(e->ev_join);
   if (e->stream2) cudaStreamDestroy(e->stream2);
@@ -1796,6 +2211,25 @@ extern "C" int b2_seq_create(b2_engine* e, int32_t reserve_tokens, int32_t* seq_
   return 0;
 }
 
+extern "C" int b2_seq_reserve(b2_engine* e, int32_t seq_id, int32_t total_tokens) {
+  B2_REQUIRE(e, "b2_seq_reserve: null engine");
+  B2_TRY(check_seq(e, seq_id));
+  Seq& s = e->seqs[seq_id];
+  B2_REQUIRE(total_tokens >= 1 && total_tokens <= e->cfg.max_model_len, "total_tokens %d outside [1, max_model_len=%d]", total_tokens,
+             e->cfg.max_model_len);
+  const int bs = e->cfg.block_size;
+  const int need = (total_tokens + bs - 1) / bs - (int)s.blocks.size();
+  if (need <= 0) return 0;
+  if (pages_available(e) < need) {
+    b2_set_error("KV pool exhausted: need %d more pages, %lld free", need, (long long)pages_available(e));
+    return -12;
+  }
+  for (int i = 0; i < need; ++i) s.blocks.push_back(take_page(e));
+  s.reserved = (int)s.blocks.size() * bs;
+  e->cur_batch.clear();  // the device copy of this sequence's block-table row is stale
+  return 0;
+}
+
 extern "C" int b2_seq_free(b2_engine* e, int32_t seq_id) {
   B2_REQUIRE(e, "b2_seq_free: null engine");
   B2_TRY(check_seq(e, seq_id));
@@ -1834,17 +2268,14 @@ extern "C" int b2_seq_truncate(b2_engine* e, int32_t seq_id, int32_t new_len) {
     B2_REQUIRE(pages_available(e) >= need, "b2_seq_truncate: no free pages to un-share %d cached pages", need);
     B2_CUDA_OK(cudaSetDevice(e->device));
     B2_CUDA_OK(cudaStreamSynchronize(e->stream));
-    const size_t blk_elems = (size_t)e->nkv * bs * e->hd;
     for (int j = first; j < (int)s.blocks.size(); ++j) {
       const int32_t old_b = s.blocks[j];
       if (e->blk_hash[old_b] == 0 && e->blk_ref[old_b] <= 1) continue;
       const int32_t nb = take_page(e);
       if (j == first && new_len % bs != 0) {
-        for (int l = 0; l < 2 * e->cfg.num_layers; ++l) {
-          bf16* base = e->kv_pool + (size_t)l * e->layer_kv_elems;
-          B2_CUDA_OK(cudaMemcpyAsync(base + (size_t)nb * blk_elems, base + (size_t)old_b * blk_elems, blk_elems * 2, cudaMemcpyDeviceToDevice,
-                                     e->stream));
-        }
+        for (const auto& rg : e->regions)
+          B2_CUDA_OK(cudaMemcpyAsync(rg.base + (size_t)nb * rg.page_bytes, rg.base + (size_t)old_b * rg.page_bytes, rg.page_bytes,
+                                     cudaMemcpyDeviceToDevice, e->stream));
       }
       s.blocks[j] = nb;
       release_page(e, old_b);
@@ -1859,8 +2290,23 @@ extern "C" int b2_seq_truncate(b2_engine* e, int32_t seq_id, int32_t new_len) {
   return 0;
 }
 
+namespace {
+int prefill_impl(b2_engine* e, const int32_t* ids, const int32_t* seq_offsets, int32_t nseq, const int32_t* seq_ids, const int32_t* rows,
+                 int32_t nrows, float* out_logits, int32_t* out_tokens);
+}
 extern "C" int b2_prefill(b2_engine* e, const int32_t* ids, const int32_t* seq_offsets, int32_t nseq, const int32_t* seq_ids,
                           int32_t* out_tokens) {
+  return prefill_impl(e, ids, seq_offsets, nseq, seq_ids, nullptr, 0, nullptr, out_tokens);
+}
+extern "C" int b2_prefill_logits(b2_engine* e, const int32_t* ids, const int32_t* seq_offsets, int32_t nseq, const int32_t* seq_ids,
+                                 const int32_t* rows, int32_t nrows, float* out_logits, int32_t* out_tokens) {
+  B2_REQUIRE(e && nrows >= 0 && (nrows == 0 || (rows && out_logits)), "b2_prefill_logits: bad arguments");
+  B2_REQUIRE(e->cfg.arch == B2_ARCH_LERASUN, "b2_prefill_logits: built for the families whose lm_head writes fp32 rows (Lerasun)");
+  return prefill_impl(e, ids, seq_offsets, nseq, seq_ids, rows, nrows, out_logits, out_tokens);
+}
+namespace {
+int prefill_impl(b2_engine* e, const int32_t* ids, const int32_t* seq_offsets, int32_t nseq, const int32_t* seq_ids, const int32_t* rows,
+                 int32_t nrows, float* out_logits, int32_t* out_tokens) {
   B2_REQUIRE(e && ids && seq_offsets && seq_ids && nseq >= 1, "b2_prefill: bad arguments");
   B2_REQUIRE(e->finalized, "b2_prefill: weights not finalized");
   B2_REQUIRE(nseq <= e->cfg.max_seqs, "b2_prefill: %d sequences > max_seqs %d", nseq, e->cfg.max_seqs);
@@ -1882,7 +2328,7 @@ extern "C" int b2_prefill(b2_engine* e, const int32_t* ids, const int32_t* seq_o
   for (int i = 0; i < nseq; ++i) {
     Seq& s = e->seqs[seq_ids[i]];
     const int n = seq_offsets[i + 1] - seq_offsets[i];
-    if (e->prefix_cache && s.len == 0 && s.chain_open && s.chain.empty()) {
+    if (e->prefix_cache && nrows == 0 && s.len == 0 && s.chain_open && s.chain.empty()) {
       skip[i] = pc_match(e, s, ids + seq_offsets[i], n);
       s.len = skip[i];  // K/V of those positions are in the pages just taken
       e->pc_queries += n;
@@ -1895,7 +2341,13 @@ extern "C" int b2_prefill(b2_engine* e, const int32_t* ids, const int32_t* seq_o
   int32_t* pos = tok + T;
   int32_t* slots = pos + T;
   int32_t* last = slots + T;
-  int32_t* bt = last + nseq;
+  int32_t* bt = last + nseq + nrows;
+  B2_REQUIRE(nrows == 0 || (nseq + nrows <= e->l_rows_cap && (size_t)(bt - e->h_stage) + (size_t)nseq * e->bt_stride <= e->h_stage_ints),
+             "b2_prefill_logits: %d rows exceed the engine's capacity", nrows);
+  for (int i = 0; i < nrows; ++i) {
+    B2_REQUIRE(rows[i] >= 0 && rows[i] < T_in, "b2_prefill_logits: row %d outside the call's %d tokens", rows[i], T_in);
+    last[nseq + i] = rows[i];  // (no prefix-cache skip in this form: rows index the tokens as given)
+  }
   int ntiles = 0, row0 = 0;
   for (int i = 0; i < nseq; ++i) {
     Seq& s = e->seqs[seq_ids[i]];
@@ -1924,14 +2376,17 @@ extern "C" int b2_prefill(b2_engine* e, const int32_t* ids, const int32_t* seq_o
   B2_CUDA_OK(cudaMemcpyAsync(e->d_tokens, tok, T * 4, cudaMemcpyHostToDevice, e->stream));
   B2_CUDA_OK(cudaMemcpyAsync(e->d_positions, pos, T * 4, cudaMemcpyHostToDevice, e->stream));
   B2_CUDA_OK(cudaMemcpyAsync(e->d_slots, slots, T * 4, cudaMemcpyHostToDevice, e->stream));
-  B2_CUDA_OK(cudaMemcpyAsync(e->d_last_rows, last, nseq * 4, cudaMemcpyHostToDevice, e->stream));
+  B2_CUDA_OK(cudaMemcpyAsync(e->d_last_rows, last, (nseq + nrows) * 4, cudaMemcpyHostToDevice, e->stream));
   B2_CUDA_OK(cudaMemcpyAsync(e->d_block_table, bt, (size_t)nseq * e->bt_stride * 4, cudaMemcpyHostToDevice, e->stream));
   B2_CUDA_OK(cudaMemcpyAsync(e->d_tiles, e->h_tiles, ntiles * sizeof(PrefillTile), cudaMemcpyHostToDevice, e->stream));
   if (e->debug_flags & 2) B2_TRY(ensure_logits(e));
   e->cur_batch.clear();
-  B2_TRY(forward(e, T, ntiles, nseq, 1));
+  B2_TRY(forward(e, T, ntiles, nseq + nrows, 1));
   // the produced tokens become the device-resident "next input" of these sequences
   B2_CUDA_OK(cudaMemcpyAsync(e->h_out, e->d_out_tokens, nseq * 4, cudaMemcpyDeviceToHost, e->stream));
+  if (nrows > 0)
+    B2_CUDA_OK(cudaMemcpyAsync(out_logits, e->l_logits + (size_t)nseq * e->cfg.vocab, (size_t)nrows * e->cfg.vocab * 4, cudaMemcpyDeviceToHost,
+                               e->stream));
   B2_CUDA_OK(cudaStreamSynchronize(e->stream));
   for (int i = 0; i < nseq; ++i) {
     Seq& s = e->seqs[seq_ids[i]];
@@ -1947,6 +2402,7 @@ extern "C" int b2_prefill(b2_engine* e, const int32_t* ids, const int32_t* seq_o
   e->last_tokens = T;
   return 0;
 }
+}  // namespace
 
 namespace {
 // Prepares device state for a decode step over seq_ids; returns padded batch B.
@@ -2107,6 +2563,7 @@ extern "C" int b2_attn_profile(b2_engine* e, int32_t nseq, const int32_t* seq_id
                                int64_t* kv_bytes_per_launch) {
   B2_REQUIRE(e && seq_ids && reps >= 1 && ms_per_launch && kv_bytes_per_launch, "b2_attn_profile: bad arguments");
   B2_CUDA_OK(cudaSetDevice(e->device));
+  B2_REQUIRE(e->cfg.arch != B2_ARCH_LERASUN, "b2_attn_profile: times the GQA decode-attention kernel; this family has none");
   B2_REQUIRE((int)e->cur_batch.size() == nseq && std::equal(seq_ids, seq_ids + nseq, e->cur_batch.begin()),
              "b2_attn_profile: run a decode step on exactly this batch first (the pass reuses its device-side page tables)");
   const b2_config& c = e->cfg;
@@ -2187,7 +2644,12 @@ extern "C" int b2_set_debug(b2_engine* e, int32_t flags) {
   B2_REQUIRE(e, "b2_set_debug: null engine");
   B2_CUDA_OK(cudaSetDevice(e->device));
   e->debug_flags = flags;
-  if ((flags & 1) && e->dbg_hidden == nullptr) {
+  if ((flags & 1) && e->cfg.arch == B2_ARCH_LERASUN) {
+    if (e->dbg_hidden_f32 == nullptr) {
+      e->dbg_cap_tokens = std::min(e->cap_tokens, 1024);
+      B2_TRY(dalloc(&e->dbg_hidden_f32, (size_t)(e->cfg.num_layers + 1) * e->dbg_cap_tokens * e->cfg.hidden));
+    }
+  } else if ((flags & 1) && e->dbg_hidden == nullptr) {
     e->dbg_cap_tokens = std::min(e->cap_tokens, 1024);
     B2_TRY(dalloc(&e->dbg_hidden, (size_t)(e->cfg.num_layers + 2) * e->dbg_cap_tokens * e->cfg.hidden));
   }
@@ -2197,6 +2659,7 @@ extern "C" int b2_set_debug(b2_engine* e, int32_t flags) {
 
 extern "C" int b2_get_hidden(b2_engine* e, int32_t layer, int32_t ntokens, uint16_t* out_bf16) {
   B2_REQUIRE(e && out_bf16, "b2_get_hidden: null argument");
+  B2_REQUIRE(e->cfg.arch != B2_ARCH_LERASUN, "b2_get_hidden: this family's residual stream is fp32 (b2_get_hidden_f32)");
   B2_REQUIRE((e->debug_flags & 1) && e->dbg_hidden, "b2_get_hidden: hidden capture not enabled (b2_set_debug(e, 1))");
   B2_REQUIRE(layer >= -1 && layer <= e->cfg.num_layers, "b2_get_hidden: layer %d out of range", layer);
   B2_REQUIRE(ntokens >= 1 && ntokens <= e->dbg_cap_tokens && ntokens <= e->last_tokens, "b2_get_hidden: ntokens %d out of range", ntokens);
@@ -2208,12 +2671,29 @@ extern "C" int b2_get_hidden(b2_engine* e, int32_t layer, int32_t ntokens, uint1
   return 0;
 }
 
+extern "C" int b2_get_hidden_f32(b2_engine* e, int32_t layer, int32_t ntokens, float* out_f32) {
+  B2_REQUIRE(e && out_f32, "b2_get_hidden_f32: null argument");
+  B2_REQUIRE((e->debug_flags & 1) && e->dbg_hidden_f32, "b2_get_hidden_f32: hidden capture not enabled, or the family's residual stream is bf16");
+  B2_REQUIRE(layer >= -1 && layer < e->cfg.num_layers, "b2_get_hidden_f32: layer %d out of range", layer);
+  B2_REQUIRE(ntokens >= 1 && ntokens <= e->dbg_cap_tokens && ntokens <= e->last_tokens, "b2_get_hidden_f32: ntokens %d out of range", ntokens);
+  B2_CUDA_OK(cudaSetDevice(e->device));
+  B2_CUDA_OK(cudaStreamSynchronize(e->stream));
+  B2_CUDA_OK(cudaMemcpy(out_f32, e->dbg_hidden_f32 + (size_t)(layer + 1) * e->dbg_cap_tokens * e->cfg.hidden, (size_t)ntokens * e->cfg.hidden * 4,
+                        cudaMemcpyDeviceToHost));
+  return 0;
+}
+
 extern "C" int b2_get_logits(b2_engine* e, int32_t nseq, float* out_logits) {
   B2_REQUIRE(e && out_logits, "b2_get_logits: null argument");
-  B2_REQUIRE((e->debug_flags & 2) && e->logits, "b2_get_logits: logits capture not enabled (b2_set_debug(e, 2))");
+  B2_REQUIRE(e->cfg.arch == B2_ARCH_LERASUN || ((e->debug_flags & 2) && e->logits), "b2_get_logits: logits capture not enabled (b2_set_debug(e, 2))");
   B2_REQUIRE(nseq >= 1 && nseq <= e->last_n, "b2_get_logits: nseq %d > sequences of the last forward (%d)", nseq, e->last_n);
   B2_CUDA_OK(cudaSetDevice(e->device));
   const size_t n = (size_t)nseq * e->cfg.vocab;
+  if (e->cfg.arch == B2_ARCH_LERASUN) {  // this family's lm_head writes fp32 rows; the leading rows are the sequences' last positions
+    B2_CUDA_OK(cudaMemcpyAsync(out_logits, e->l_logits, n * 4, cudaMemcpyDeviceToHost, e->stream));
+    B2_CUDA_OK(cudaStreamSynchronize(e->stream));
+    return 0;
+  }
   float* tmp = nullptr;
   B2_TRY(dalloc(&tmp, n));
   int rc = launch_logits_to_f32(e->logits, tmp, n, e->stream);
@@ -2252,7 +2732,7 @@ extern "C" int b2_sample(b2_engine* e, int32_t nseq, const b2_sampling* params, 
     if (params->seed != 0 && sd == 0) sd = 1;
     e->h_sample_rows[i] = SampleRow{i, params->temperature, params->top_k, params->top_p, sd};
   }
-  B2_TRY(launch_sample_rows(e->logits, e->h_sample_rows.data(), e->d_sample_rows, e->d_out_tokens, nseq, e->cfg.vocab, (uint64_t)e->launches,
+  B2_TRY(launch_sample_rows(e->logits, e->h_sample_rows.data(), e->d_sample_rows, e->d_out_tokens, nseq, e->v_pad > 0 ? e->v_pad : e->cfg.vocab, (uint64_t)e->launches,
                             e->stream));
   e->launches++;
   B2_CUDA_OK(cudaMemcpyAsync(e->h_out, e->d_out_tokens, nseq * 4, cudaMemcpyDeviceToHost, e->stream));
@@ -2272,7 +2752,7 @@ extern "C" int b2_sample_rows(b2_engine* e, int32_t nrows, const int32_t* rows, 
     e->h_sample_rows[i] = SampleRow{rows[i], params[i].temperature, params[i].top_k, params[i].top_p, params[i].seed};
   }
   // one launch for all rows (the host vector outlives the copy: the call synchronises below)
-  B2_TRY(launch_sample_rows(e->logits, e->h_sample_rows.data(), e->d_sample_rows, e->d_sample_out, nrows, e->cfg.vocab, (uint64_t)e->launches,
+  B2_TRY(launch_sample_rows(e->logits, e->h_sample_rows.data(), e->d_sample_rows, e->d_sample_out, nrows, e->v_pad > 0 ? e->v_pad : e->cfg.vocab, (uint64_t)e->launches,
                             e->stream));
   e->launches++;
   B2_CUDA_OK(cudaMemcpyAsync(e->h_out, e->d_sample_out, nrows * 4, cudaMemcpyDeviceToHost, e->stream));

@@ -1,0 +1,162 @@
+// gemm_any.cu -- C = A . W^T for operands of ANY shape and either precision (bf16 or fp32 elements, fp32 accumulation
+// by plain fused multiply-adds: no reduced-precision matrix mode), as one strided batch or as ragged groups.
+//
+// The tcgen05 projections (gemm_tc.cu and friends) are built for bf16 operands whose sizes are multiples of their tiles.
+// Models with a layer list bring shapes that are not (a latent of 96, 12 experts of 80 rows, a vocabulary of 500), a
+// true-fp32 mode, per-head products against a slice of a wider activation row, and experts that each see their own
+// subset of the tokens.  This kernel takes all of them:
+//   * strided batch: blockIdx.z picks (A + z * a_bs, W + z * w_bs, C + z * c_bs): one launch for all heads of an
+//     absorbed-query or value up-projection;
+//   * ragged groups (routed experts): a device-built list of row tiles, each belonging to one group; rows of a group are
+//     slots [group_offsets[g], group_offsets[g + 1]) of a token permutation, A rows are gathered through a_rows (slot ->
+//     row of A) and the group's weights start at W + g * w_bs;
+//   * epilogues: store (fp32 or bf16), squared ReLU then store, or add into an fp32 C (the residual stream).
+// Tile 64 x 64 x 16, 256 threads, 4 x 4 outputs per thread, operands staged in shared memory as fp32; every global
+// access is bounds-checked, so no size needs padding.  Rows of one output are summed in k order by one thread: the
+// result of a row does not depend on which other rows share its tile.
+#include "kernels.h"
+
+namespace b2 {
+
+namespace {
+
+constexpr int BM = 64, BN = 64, BK = 16;
+
+template <typename T>
+__device__ __forceinline__ float ldf(const T* p);
+template <>
+__device__ __forceinline__ float ldf<float>(const float* p) { return *p; }
+template <>
+__device__ __forceinline__ float ldf<bf16>(const bf16* p) { return __bfloat162float(*p); }
+
+template <typename TA, typename TW, typename TC>
+__global__ void __launch_bounds__(256) gemm_any_kernel(AnyGemm g) {
+  __shared__ float As[BK][BM + 4];
+  __shared__ float Ws[BK][BN + 4];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int tid = threadIdx.x;
+  const TA* A = reinterpret_cast<const TA*>(g.A);
+  const TW* W = reinterpret_cast<const TW*>(g.W);
+  TC* C = reinterpret_cast<TC*>(g.C);
+  int row0, row_end;  // slots (ragged) or rows (dense) of this tile
+  if (g.tile_group != nullptr) {
+    if ((int)blockIdx.x >= *g.n_tiles) return;
+    const int grp = g.tile_group[blockIdx.x];
+    row0 = g.tile_row0[blockIdx.x];
+    row_end = min(row0 + BM, g.group_offsets[grp + 1]);
+    W += (size_t)grp * g.w_bs;
+  } else {
+    row0 = blockIdx.x * BM;
+    row_end = min(row0 + BM, g.M);
+    A += (size_t)blockIdx.z * g.a_bs;
+    W += (size_t)blockIdx.z * g.w_bs;
+    C += (size_t)blockIdx.z * g.c_bs;
+  }
+  const int n0 = blockIdx.y * BN;
+  // loader mapping: thread -> (row r of the tile, 4 consecutive k)
+  const int lr = tid >> 2, lk = (tid & 3) * 4;
+  long a_row = -1;
+  if (row0 + lr < row_end) a_row = g.a_rows ? (long)g.a_rows[row0 + lr] : (long)(row0 + lr);
+  const long w_row = (n0 + lr < g.N) ? (long)(n0 + lr) : -1;
+  const int tx = tid & 15, ty = tid >> 4;  // outputs: rows ty*4.., cols tx*4..
+  float acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+  for (int k0 = 0; k0 < g.K; k0 += BK) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int k = k0 + lk + j;
+      As[lk + j][lr] = (a_row >= 0 && k < g.K) ? ldf(A + a_row * g.lda + k) : 0.f;
+      Ws[lk + j][lr] = (w_row >= 0 && k < g.K) ? ldf(W + w_row * g.ldw + k) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < BK; ++k) {
+      const float4 a = *reinterpret_cast<const float4*>(&As[k][ty * 4]);
+      const float4 w = *reinterpret_cast<const float4*>(&Ws[k][tx * 4]);
+      const float av[4] = {a.x, a.y, a.z, a.w}, wv[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(av[i], wv[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int r = row0 + ty * 4 + i;
+    if (r >= row_end) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = n0 + tx * 4 + j;
+      if (n >= g.N) continue;
+      float v = acc[i][j] * g.alpha;
+      TC* dst = C + (size_t)r * g.ldc + n;
+      if (g.epilogue == ANY_EPI_RELU2) {
+        v = fmaxf(v, 0.f);
+        v = v * v;
+      }
+      if (g.epilogue == ANY_EPI_ADD) {
+        if constexpr (sizeof(TC) == 4) *dst = (TC)((float)*dst + v);
+      } else {
+        if constexpr (sizeof(TC) == 4) *dst = v;
+        else *dst = __float2bfloat16_rn(v);
+      }
+    }
+  }
+}
+
+// One CTA: tiles of the ragged groups.  group_offsets [G + 1] -> (tile_group, tile_row0, n_tiles).
+__global__ void ragged_tiles_kernel(const int* __restrict__ group_offsets, int G, int* __restrict__ tile_group, int* __restrict__ tile_row0,
+                                    int* __restrict__ n_tiles, int cap) {
+  pdl_wait();
+  pdl_launch_dependents();
+  if (threadIdx.x != 0) return;
+  int n = 0;
+  for (int g = 0; g < G; ++g)
+    for (int r = group_offsets[g]; r < group_offsets[g + 1] && n < cap; r += BM) {
+      tile_group[n] = g;
+      tile_row0[n] = r;
+      ++n;
+    }
+  *n_tiles = n;
+}
+
+}  // namespace
+
+int any_gemm_tile_rows() { return BM; }
+
+int launch_ragged_tiles(const int* group_offsets, int G, int* tile_group, int* tile_row0, int* n_tiles, int cap, cudaStream_t s) {
+  B2_CUDA_OK(b2_launch(ragged_tiles_kernel, dim3(1), dim3(32), 0, s, group_offsets, G, tile_group, tile_row0, n_tiles, cap));
+  return 0;
+}
+
+int launch_gemm_any(const AnyGemm& g, int a_f32, int w_f32, int c_f32, int batch, int max_tiles, cudaStream_t s) {
+  if (g.N <= 0 || g.K <= 0) return 0;
+  B2_REQUIRE(g.epilogue != ANY_EPI_ADD || c_f32, "gemm_any: the add epilogue needs an fp32 C");
+  dim3 grid;
+  if (g.tile_group != nullptr) {
+    if (max_tiles <= 0) return 0;
+    grid = dim3(max_tiles, (g.N + BN - 1) / BN, 1);
+  } else {
+    if (g.M <= 0) return 0;
+    grid = dim3((g.M + BM - 1) / BM, (g.N + BN - 1) / BN, batch > 0 ? batch : 1);
+  }
+#define GA(TA, TW, TC) B2_CUDA_OK(b2_launch(gemm_any_kernel<TA, TW, TC>, grid, dim3(256), 0, s, g))
+  if (a_f32 && w_f32 && c_f32) GA(float, float, float);
+  else if (!a_f32 && !w_f32 && c_f32) GA(bf16, bf16, float);
+  else if (!a_f32 && !w_f32 && !c_f32) GA(bf16, bf16, bf16);
+  else if (a_f32 && !w_f32 && c_f32) GA(float, bf16, float);
+  else if (a_f32 && !w_f32 && !c_f32) GA(float, bf16, bf16);
+  else {
+    b2_set_error("gemm_any: operand type combination (%d, %d, %d) not built", a_f32, w_f32, c_f32);
+    return -22;
+  }
+#undef GA
+  return 0;
+}
+
+}  // namespace b2

@@ -214,4 +214,72 @@ int launch_sample_rows(const bf16* logits, const SampleRow* rows_host, SampleRow
 
 int device_num_sms();
 
+// ---- gemm_any.cu: C = A . W^T for any shape, bf16 or fp32 operands, strided batch or ragged groups ----
+enum AnyEpilogue { ANY_EPI_STORE = 0, ANY_EPI_RELU2 = 1, ANY_EPI_ADD = 2 };
+struct AnyGemm {
+  const void* A = nullptr;   // [rows][lda]
+  const void* W = nullptr;   // [N][ldw]
+  void* C = nullptr;         // [rows][ldc]
+  int M = 0, N = 0, K = 0;   // dense: M rows; ragged: M unused
+  long lda = 0, ldw = 0, ldc = 0;
+  long a_bs = 0, w_bs = 0, c_bs = 0;      // element strides between batches (dense) / between groups' weights (ragged: w_bs)
+  const int* tile_group = nullptr;        // ragged: device lists built by launch_ragged_tiles
+  const int* tile_row0 = nullptr;
+  const int* n_tiles = nullptr;
+  const int* group_offsets = nullptr;     // [groups + 1] slots of each group
+  const int* a_rows = nullptr;            // slot -> row of A (null: the slot itself)
+  int epilogue = ANY_EPI_STORE;
+  float alpha = 1.f;
+};
+int any_gemm_tile_rows();
+int launch_ragged_tiles(const int* group_offsets, int G, int* tile_group, int* tile_row0, int* n_tiles, int cap, cudaStream_t s);
+// *_f32: element type of A / W / C (1 = fp32, 0 = bf16); batch: strided batches (dense); max_tiles: capacity of the tile list (ragged)
+int launch_gemm_any(const AnyGemm& g, int a_f32, int w_f32, int c_f32, int batch, int max_tiles, cudaStream_t s);
+
+// ---- resid_f32.cu: an fp32 residual stream and the unit-offset RMS norm x / rms(x) * (1 + g) around it ----
+// gains are fp32 and hold 1 + g already.  Outputs are fp32 or bf16 (x_f32).
+int launch_embed_unit_norm(const int32_t* ids, const void* table, int table_f32, const float* gain1p, float* h, int T, int W, int vocab,
+                           float eps, cudaStream_t s);
+// x1 = norm(h) * gain_a, x2 = norm(h) * gain_b (x2 / gain_b may be null): both norms of one layer share the statistic.
+// rows != null: normalise rows[i] of h into row i of x1 (the final norm over the rows that get logits).
+int launch_unit_norm2(const float* h, const float* gain_a, const float* gain_b, void* x1, void* x2, int x_f32, int T, int W, float eps,
+                      const int32_t* rows, cudaStream_t s);
+// fp32 logits (row stride V) -> greedy token per row (lowest index on ties), and optionally bf16 rows of stride v_pad
+// whose tail is -inf (what the sampler reads; only the first bf16_rows rows)
+int launch_logits_finish(const float* logits, int32_t* out_tokens, bf16* logits_bf16, int bf16_rows, int rows, int V, int v_pad, cudaStream_t s);
+
+// ---- attn_latent.cu: attention over a shared per-token latent (absorbed form) ----
+// The cache holds, per token, the normalised latent c [kv_rank] and the rotated key piece [rot_dim] side by side
+// (row width kv_rank + rot_dim, element type fp32 or bf16), in pages of block_size tokens.
+struct LatentGeom {
+  int heads, dim, rot_dim, vdim, kv_rank, rot_dims;
+  float rot_base, scale, eps;
+};
+// qd [T][ld] fp32 = the fused projection's output: per head [dim | rot_dim], then (has_kv) the latent and the key piece.
+// Writes q_nope [T][heads*dim] (operand type), q_rot [T][heads*rot_dim] fp32 (rotated) and, when has_kv, the token's cache row.
+int launch_latent_finish(const float* qd, int ld, const LatentGeom& g, int has_kv, const float* latent_gain, const int32_t* positions,
+                         const int32_t* slots, void* q_nope, int x_f32, float* q_rot, void* cache, int cache_f32, int T, cudaStream_t s);
+// scores and weighted latent sum: q_abs [T][heads][kv_rank] fp32 (query pulled through the key up-projection), q_rot as above;
+// tiles == null: decode form (token i is the newest token of block-table row i at positions[i]; seq_lens[i] == 0 rows are empty).
+// out_lat [T][heads][kv_rank] (operand type).
+int launch_latent_attention(const float* q_abs, const float* q_rot, const void* cache, int cache_f32, const LatentGeom& g,
+                            const int32_t* block_table, int bt_stride, int block_size, const PrefillTile* tiles, int ntiles,
+                            const int32_t* positions, const int32_t* seq_lens, const float* sink, void* out_lat, int x_f32, int T,
+                            cudaStream_t s);
+
+// ---- moe_route.cu: sigmoid router with a choice offset and grouped selection, and the token permutation by expert ----
+struct RouteGeom {
+  int experts, top, groups, keep;
+};
+// x [T][W] (operand type), router [experts][W] fp32, correction [experts] fp32 -> idx [T][top], weight [T][top]
+int launch_route(const void* x, int x_f32, const float* router, const float* correction, const RouteGeom& g, int32_t* idx, float* weight,
+                 int T, int W, cudaStream_t s);
+// counting sort of the T*top (token, choice) pairs by expert: offsets [experts + 1], slot_token [T*top] (slot -> token),
+// pair_slot [T*top] (pair -> slot).  Deterministic: pairs of an expert keep their (token, choice) order.
+int launch_route_permute(const int32_t* idx, int T, int top, int experts, int32_t* offsets, int32_t* slot_token, int32_t* pair_slot,
+                         cudaStream_t s);
+// h[t] += sum_k weight[t][k] * y[pair_slot[t*top + k]]   (+ mix[t] when given); fp32
+int launch_route_combine(float* h, const float* mix, const float* y, const float* weight, const int32_t* pair_slot, int T, int W, int top,
+                         cudaStream_t s);
+
 }  // namespace b2

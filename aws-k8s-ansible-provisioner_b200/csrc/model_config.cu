@@ -1,0 +1,201 @@
+// model_config.cu -- the model registry: MODEL_DIR/config.json -> b2_config (+ the layer list of the families that have
+// one).  b2serve, the Python mirror and bin/trace_run all choose the model class through this one function, so a family
+// is added to the framework here, in b2_engine_create and nowhere else.  Host code only.
+//
+// HF families are told apart by "model_type" (the keys follow HF's Qwen3Config / Phi3Config / OPTConfig); Lerasun by
+// "architecture": "Lerasun", whose config lists its layers one by one:
+//   {"architecture": "Lerasun", "vocab": V, "width": W, "logit_scale": s, "norm": {"eps": e},
+//    "layers": [{"type": "latent_attention",
+//                "mixer": {"heads", "dim", "rot_dim", "vdim", "kv_rank", "scale", "rot": {"base", "dims"}, "kv_from"?},
+//                "mlp": null | {"kind": "moe", "expert": {"ff"}, "router": {"experts", "top", "groups": {"count", "keep"}}}}, ...]}
+#include <fstream>
+#include <sstream>
+#include <string>
+
+#include "../../include/b2_engine.h"
+#include "common.cuh"
+#include "json.hpp"
+
+using b2json::Value;
+
+namespace {
+
+int need_int(const Value& o, const char* key, const char* where, int* out) {
+  const Value* v = o.find(key);
+  if (!v || !v->is_number()) {
+    b2_set_error("config.json: %s.%s missing or not a number", where, key);
+    return -22;
+  }
+  *out = (int)v->as_int();
+  return 0;
+}
+int need_float(const Value& o, const char* key, const char* where, float* out) {
+  const Value* v = o.find(key);
+  if (!v || !v->is_number()) {
+    b2_set_error("config.json: %s.%s missing or not a number", where, key);
+    return -22;
+  }
+  *out = (float)v->as_double();
+  return 0;
+}
+#define CFG_TRY(expr)       \
+  do {                      \
+    int _r = (expr);        \
+    if (_r != 0) return _r; \
+  } while (0)
+
+int lerasun_config(const Value& j, b2_config* c, b2_layer_spec* specs, int max_specs) {
+  c->arch = B2_ARCH_LERASUN;
+  CFG_TRY(need_int(j, "vocab", "config", &c->vocab));
+  CFG_TRY(need_int(j, "width", "config", &c->hidden));
+  const Value* norm = j.find("norm");
+  if (!norm || !norm->is_object()) {
+    b2_set_error("config.json: norm missing");
+    return -22;
+  }
+  CFG_TRY(need_float(*norm, "eps", "norm", &c->rms_eps));
+  c->logit_scale = 1.0f;
+  if (const Value* ls = j.find("logit_scale"))
+    if (ls->is_number()) c->logit_scale = (float)ls->as_double();
+  const Value* layers = j.find("layers");
+  if (!layers || !layers->is_array() || layers->size() == 0) {
+    b2_set_error("config.json: layers missing or empty");
+    return -22;
+  }
+  c->num_layers = (int)layers->size();
+  if (c->num_layers > max_specs || specs == nullptr) {
+    b2_set_error("config.json: %d layers, room for %d layer specs", c->num_layers, max_specs);
+    return -22;
+  }
+  for (int i = 0; i < c->num_layers; ++i) {
+    const Value& L = layers->at(i);
+    b2_layer_spec& s = specs[i];
+    memset(&s, 0, sizeof s);
+    char where[48];
+    snprintf(where, sizeof where, "layers[%d].mixer", i);
+    const Value* type = L.find("type");
+    const Value* m = L.find("mixer");
+    if (!type || !type->is_string() || !m || !m->is_object()) {
+      b2_set_error("config.json: layers[%d] needs type and mixer", i);
+      return -22;
+    }
+    if (type->as_string() != "latent_attention") {
+      b2_set_error("config.json: layers[%d]: mixer type '%s' not built (latent_attention)", i, type->as_string().c_str());
+      return -22;
+    }
+    s.mixer = B2_MIXER_LATENT_ATTENTION;
+    CFG_TRY(need_int(*m, "heads", where, &s.heads));
+    CFG_TRY(need_int(*m, "dim", where, &s.dim));
+    CFG_TRY(need_int(*m, "rot_dim", where, &s.rot_dim));
+    CFG_TRY(need_int(*m, "vdim", where, &s.vdim));
+    CFG_TRY(need_int(*m, "kv_rank", where, &s.kv_rank));
+    CFG_TRY(need_float(*m, "scale", where, &s.scale));
+    const Value* rot = m->find("rot");
+    if (!rot || !rot->is_object()) {
+      b2_set_error("config.json: %s.rot missing", where);
+      return -22;
+    }
+    CFG_TRY(need_float(*rot, "base", where, &s.rot_base));
+    CFG_TRY(need_int(*rot, "dims", where, &s.rot_dims));
+    s.kv_from = -1;
+    if (const Value* kf = m->find("kv_from"))
+      if (kf->is_number()) s.kv_from = (int)kf->as_int();
+    const Value* mlp = L.find("mlp");
+    s.ff = B2_FF_NONE;
+    if (mlp && mlp->is_object()) {
+      snprintf(where, sizeof where, "layers[%d].mlp", i);
+      const Value* kind = mlp->find("kind");
+      if (!kind || !kind->is_string() || kind->as_string() != "moe") {
+        b2_set_error("config.json: %s.kind '%s' not built (moe)", where, kind && kind->is_string() ? kind->as_string().c_str() : "?");
+        return -22;
+      }
+      s.ff = B2_FF_ROUTED_EXPERTS;
+      const Value* ex = mlp->find("expert");
+      const Value* ro = mlp->find("router");
+      if (!ex || !ex->is_object() || !ro || !ro->is_object()) {
+        b2_set_error("config.json: %s needs expert and router", where);
+        return -22;
+      }
+      CFG_TRY(need_int(*ex, "ff", where, &s.ff_dim));
+      CFG_TRY(need_int(*ro, "experts", where, &s.experts));
+      CFG_TRY(need_int(*ro, "top", where, &s.top));
+      s.groups = 1;
+      s.groups_keep = 1;
+      if (const Value* gr = ro->find("groups"))
+        if (gr->is_object()) {
+          CFG_TRY(need_int(*gr, "count", where, &s.groups));
+          CFG_TRY(need_int(*gr, "keep", where, &s.groups_keep));
+        }
+    }
+  }
+  c->layer_specs = specs;
+  c->tie_embeddings = 0;
+  // the GQA fields describe nothing in this family
+  c->num_q_heads = c->num_kv_heads = 0;
+  c->head_dim = c->intermediate = 0;
+  return 0;
+}
+
+}  // namespace
+
+extern "C" int b2_config_from_dir(const char* model_dir, b2_config* c, b2_layer_spec* specs, int32_t max_specs) {
+  B2_REQUIRE(model_dir && c, "b2_config_from_dir: null argument");
+  const std::string path = std::string(model_dir) + "/config.json";
+  std::ifstream f(path, std::ios::binary);
+  if (!f) {
+    b2_set_error("cannot open %s", path.c_str());
+    return -2;
+  }
+  std::stringstream ss;
+  ss << f.rdbuf();
+  Value j;
+  try {
+    j = b2json::parse(ss.str());
+  } catch (const std::exception& ex) {
+    b2_set_error("%s: %s", path.c_str(), ex.what());
+    return -22;
+  }
+  c->abi_version = B2_ABI_VERSION;
+  c->layer_specs = nullptr;
+  c->logit_scale = 0.f;
+  const Value* archv = j.find("architecture");
+  if (archv && archv->is_string()) {
+    if (archv->as_string() == "Lerasun") return lerasun_config(j, c, specs, max_specs);
+    b2_set_error("%s: architecture '%s' not built", path.c_str(), archv->as_string().c_str());
+    return -22;
+  }
+  // ---- HF families ----
+  auto geti = [&](const char* k, int d) { const Value* v = j.find(k); return v && v->is_number() ? (int)v->as_int() : d; };
+  auto getf = [&](const char* k, double d) { const Value* v = j.find(k); return v && v->is_number() ? v->as_double() : d; };
+  c->arch = B2_ARCH_QWEN3;
+  c->num_layers = geti("num_hidden_layers", c->num_layers);
+  c->hidden = geti("hidden_size", c->hidden);
+  c->num_q_heads = geti("num_attention_heads", c->num_q_heads);
+  c->num_kv_heads = geti("num_key_value_heads", c->num_kv_heads);
+  c->head_dim = geti("head_dim", c->hidden / (c->num_q_heads > 0 ? c->num_q_heads : 1));
+  c->intermediate = geti("intermediate_size", c->intermediate);
+  c->vocab = geti("vocab_size", c->vocab);
+  const Value* tie = j.find("tie_word_embeddings");
+  if (tie && tie->is_bool()) c->tie_embeddings = tie->b ? 1 : 0;
+  c->rms_eps = (float)getf("rms_norm_eps", c->rms_eps);
+  double theta = getf("rope_theta", c->rope_theta);
+  const Value* rp = j.find("rope_parameters");
+  if (rp && rp->find("rope_theta")) theta = rp->find("rope_theta")->as_double(theta);
+  c->rope_theta = (float)theta;
+  const Value* mt = j.find("model_type");
+  if (mt && mt->is_string() && mt->as_string() == "phi3") {
+    c->arch = B2_ARCH_PHI3;
+    c->rotary_dim = (int)(getf("partial_rotary_factor", 1.0) * c->head_dim + 0.5);
+    c->sliding_window = geti("sliding_window", 0);  // null in the config parses as "not a number" -> 0
+  } else if (mt && mt->is_string() && mt->as_string() == "opt") {
+    // HF OPTConfig names: ffn_dim, no kv-head count (MHA), LayerNorm eps is torch's default
+    c->arch = B2_ARCH_OPT;
+    c->num_kv_heads = c->num_q_heads;
+    c->head_dim = c->hidden / (c->num_q_heads > 0 ? c->num_q_heads : 1);
+    c->intermediate = geti("ffn_dim", c->intermediate);
+    c->max_positions = geti("max_position_embeddings", 2048);
+    c->rms_eps = 1e-5f;
+    c->tie_embeddings = 1;
+  }
+  return 0;
+}

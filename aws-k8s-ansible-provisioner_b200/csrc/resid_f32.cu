@@ -1,0 +1,138 @@
+// resid_f32.cu -- element-wise kernels around an fp32 residual stream: the embedding lookup with its norm, the
+// unit-offset RMS norm  x / sqrt(mean(x^2) + eps) * (1 + g)  that feeds both branches of a parallel layer from ONE
+// statistic, and the tail of the lm_head (greedy token, the sampler's bf16 rows).
+//
+// The bf16 families keep their residual stream in bf16 (elementwise.cu reproduces HF's rounding points); families that
+// ask for an fp32 stream (Lerasun) use these.  Statistics, gains and the stream itself are fp32 throughout; only the
+// operand handed to the next projection is rounded to bf16, and not even that when the engine runs in fp32.
+// One CTA of 128 threads per token row; any width.
+#include "kernels.h"
+
+namespace b2 {
+
+namespace {
+
+__device__ __forceinline__ float block_sum_128(float v, float* red) {
+  v = warp_sum(v);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+  __syncthreads();
+  const float r = red[0] + red[1] + red[2] + red[3];
+  __syncthreads();
+  return r;
+}
+
+template <typename TT>
+__global__ void __launch_bounds__(128) embed_unit_norm_kernel(const int32_t* __restrict__ ids, const TT* __restrict__ table,
+                                                              const float* __restrict__ gain1p, float* __restrict__ h, int W, int vocab,
+                                                              float eps) {
+  __shared__ float red[4];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int t = blockIdx.x;
+  int id = ids[t];
+  id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
+  const TT* row = table + (size_t)id * W;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < W; i += 128) {
+    const float v = (float)row[i];
+    ss = fmaf(v, v, ss);
+  }
+  ss = block_sum_128(ss, red);
+  const float r = 1.0f / sqrtf(ss / (float)W + eps);
+  for (int i = threadIdx.x; i < W; i += 128) h[(size_t)t * W + i] = (float)row[i] * r * gain1p[i];
+}
+
+template <typename TX>
+__global__ void __launch_bounds__(128) unit_norm2_kernel(const float* __restrict__ h, const float* __restrict__ gain_a,
+                                                         const float* __restrict__ gain_b, TX* __restrict__ x1, TX* __restrict__ x2, int W,
+                                                         float eps, const int32_t* __restrict__ rows) {
+  __shared__ float red[4];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int t = blockIdx.x;
+  const float* src = h + (size_t)(rows ? rows[t] : t) * W;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < W; i += 128) {
+    const float v = src[i];
+    ss = fmaf(v, v, ss);
+  }
+  ss = block_sum_128(ss, red);
+  const float r = 1.0f / sqrtf(ss / (float)W + eps);
+  for (int i = threadIdx.x; i < W; i += 128) {
+    const float v = src[i] * r;
+    x1[(size_t)t * W + i] = (TX)(v * gain_a[i]);
+    if (x2 != nullptr) x2[(size_t)t * W + i] = (TX)(v * gain_b[i]);
+  }
+}
+
+__global__ void __launch_bounds__(256) logits_finish_kernel(const float* __restrict__ logits, int32_t* __restrict__ out_tokens,
+                                                            bf16* __restrict__ lb, int lb_rows, int V, int v_pad) {
+  __shared__ float bv[8];
+  __shared__ int bi[8];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int r = blockIdx.x;
+  if (r >= lb_rows) lb = nullptr;
+  const float* row = logits + (size_t)r * V;
+  float best = -INFINITY;
+  int besti = 0x7fffffff;
+  for (int i = threadIdx.x; i < v_pad; i += 256) {
+    const float v = i < V ? row[i] : -INFINITY;
+    if (lb != nullptr) lb[(size_t)r * v_pad + i] = __float2bfloat16_rn(v);
+    if (i < V && (v > best || (v == best && i < besti))) {
+      best = v;
+      besti = i;
+    }
+  }
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, besti, o);
+    if (ov > best || (ov == best && oi < besti)) {
+      best = ov;
+      besti = oi;
+    }
+  }
+  if ((threadIdx.x & 31) == 0) {
+    bv[threadIdx.x >> 5] = best;
+    bi[threadIdx.x >> 5] = besti;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < 8; ++w)
+      if (bv[w] > best || (bv[w] == best && bi[w] < besti)) {
+        best = bv[w];
+        besti = bi[w];
+      }
+    out_tokens[r] = besti == 0x7fffffff ? 0 : besti;
+  }
+}
+
+}  // namespace
+
+int launch_embed_unit_norm(const int32_t* ids, const void* table, int table_f32, const float* gain1p, float* h, int T, int W, int vocab,
+                           float eps, cudaStream_t s) {
+  if (T <= 0) return 0;
+  if (table_f32)
+    B2_CUDA_OK(b2_launch(embed_unit_norm_kernel<float>, dim3(T), dim3(128), 0, s, ids, (const float*)table, gain1p, h, W, vocab, eps));
+  else
+    B2_CUDA_OK(b2_launch(embed_unit_norm_kernel<bf16>, dim3(T), dim3(128), 0, s, ids, (const bf16*)table, gain1p, h, W, vocab, eps));
+  return 0;
+}
+
+int launch_unit_norm2(const float* h, const float* gain_a, const float* gain_b, void* x1, void* x2, int x_f32, int T, int W, float eps,
+                      const int32_t* rows, cudaStream_t s) {
+  if (T <= 0) return 0;
+  if (x_f32)
+    B2_CUDA_OK(b2_launch(unit_norm2_kernel<float>, dim3(T), dim3(128), 0, s, h, gain_a, gain_b, (float*)x1, (float*)x2, W, eps, rows));
+  else
+    B2_CUDA_OK(b2_launch(unit_norm2_kernel<bf16>, dim3(T), dim3(128), 0, s, h, gain_a, gain_b, (bf16*)x1, (bf16*)x2, W, eps, rows));
+  return 0;
+}
+
+int launch_logits_finish(const float* logits, int32_t* out_tokens, bf16* logits_bf16, int bf16_rows, int rows, int V, int v_pad, cudaStream_t s) {
+  if (rows <= 0) return 0;
+  B2_CUDA_OK(b2_launch(logits_finish_kernel, dim3(rows), dim3(256), 0, s, logits, out_tokens, logits_bf16, bf16_rows, V, v_pad));
+  return 0;
+}
+
+}  // namespace b2

@@ -60,6 +60,7 @@ struct Options {
   int device = 0;
   int use_graphs = 1;
   bool prefix_caching = false;  // --enable-prefix-caching
+  bool f32 = false;             // --dtype float32: families with an fp32 path (Lerasun) compute in true fp32
 };
 
 static void usage() {
@@ -104,9 +105,10 @@ static bool parse_args(int argc, char** argv, Options& o) {
     else if (key == "--tokenizer") o.tokenizer_path = V("--tokenizer");
     else if (key == "--enable-prefix-caching") o.prefix_caching = true;
     else if (key == "--no-enable-prefix-caching") o.prefix_caching = false;
-    else if (key == "--dtype" || key == "--tensor-parallel-size" || key == "--trust-remote-code" || key == "--disable-log-requests" ||
+    else if (key == "--dtype") { const std::string d = V("--dtype"); o.f32 = (d == "float32" || d == "float"); }
+    else if (key == "--tensor-parallel-size" || key == "--trust-remote-code" || key == "--disable-log-requests" ||
              key == "--kv-cache-dtype" || key == "--download-dir") {
-      // accepted for chart compatibility; this build is bf16, one GPU per replica
+      // accepted for chart compatibility; one GPU per replica
       if (!has_inl && key != "--trust-remote-code" && key != "--disable-log-requests" && i + 1 < argc) ++i;
     } else if (a.rfind("--", 0) == 0) { fprintf(stderr, "b2serve: unknown flag %s\n", a.c_str()); return false; }
     else if (a == "serve") continue;  // `vllm serve MODEL` style
@@ -135,41 +137,13 @@ static void fill_config(const Options& o, b2_config& c) {
   // Qwen3-0.6B (BASELINE.json north_star) unless the model directory carries a config.json
   c.num_layers = 28; c.hidden = 1024; c.num_q_heads = 16; c.num_kv_heads = 8; c.head_dim = 128; c.intermediate = 3072;
   c.vocab = 151936; c.tie_embeddings = 1; c.rms_eps = 1e-6f; c.rope_theta = 1e6f;
-  if (is_dir(o.model) && is_file(o.model + "/config.json")) {
-    Value j = b2json::parse(read_file(o.model + "/config.json"));
-    auto geti = [&](const char* k, int d) { const Value* v = j.find(k); return v && v->is_number() ? (int)v->as_int() : d; };
-    auto getf = [&](const char* k, double d) { const Value* v = j.find(k); return v && v->is_number() ? v->as_double() : d; };
-    c.num_layers = geti("num_hidden_layers", c.num_layers);
-    c.hidden = geti("hidden_size", c.hidden);
-    c.num_q_heads = geti("num_attention_heads", c.num_q_heads);
-    c.num_kv_heads = geti("num_key_value_heads", c.num_kv_heads);
-    c.head_dim = geti("head_dim", c.hidden / std::max(1, c.num_q_heads));
-    c.intermediate = geti("intermediate_size", c.intermediate);
-    c.vocab = geti("vocab_size", c.vocab);
-    const Value* tie = j.find("tie_word_embeddings");
-    if (tie && tie->is_bool()) c.tie_embeddings = tie->b ? 1 : 0;
-    c.rms_eps = (float)getf("rms_norm_eps", c.rms_eps);
-    double theta = getf("rope_theta", c.rope_theta);
-    const Value* rp = j.find("rope_parameters");
-    if (rp && rp->find("rope_theta")) theta = rp->find("rope_theta")->as_double(theta);
-    c.rope_theta = (float)theta;
-    // model family: "model_type" of the HF config.json (qwen3 / phi3)
-    const Value* mt = j.find("model_type");
-    if (mt && mt->is_string() && mt->as_string() == "phi3") {
-      c.arch = B2_ARCH_PHI3;
-      c.rotary_dim = (int)(getf("partial_rotary_factor", 1.0) * c.head_dim + 0.5);
-      c.sliding_window = geti("sliding_window", 0);  // null in the config parses as "not a number" -> 0
-    } else if (mt && mt->is_string() && mt->as_string() == "opt") {
-      // HF OPTConfig names: ffn_dim, no kv-head count (MHA), LayerNorm eps is torch's default
-      c.arch = B2_ARCH_OPT;
-      c.num_kv_heads = c.num_q_heads;
-      c.head_dim = c.hidden / std::max(1, c.num_q_heads);
-      c.intermediate = geti("ffn_dim", c.intermediate);
-      c.max_positions = geti("max_position_embeddings", 2048);
-      c.rms_eps = 1e-5f;
-      c.tie_embeddings = 1;
-    }
+  // the model registry of the engine library reads the directory's config.json and picks the family
+  static b2_layer_spec specs[1024];  // outlives b2_engine_create, which copies the list
+  if (is_dir(o.model) && is_file(o.model + "/config.json") && b2_config_from_dir(o.model.c_str(), &c, specs, 1024) != 0) {
+    fprintf(stderr, "b2serve: %s\n", b2_last_error());
+    exit(1);
   }
+  c.compute_f32 = (o.f32 && c.arch == B2_ARCH_LERASUN) ? 1 : 0;  // the other families have no fp32 path: the flag is accepted and ignored
   c.max_model_len = o.max_model_len;
   c.block_size = o.block_size;
   c.num_blocks = o.num_blocks;
@@ -188,6 +162,10 @@ static uint16_t f2bf(float f) {
 
 // HF default init statistics: N(0, 0.02) for Linear/Embedding, ones for norm gains.
 static int load_dummy_weights(b2_engine* e, const b2_config& c, uint64_t seed) {
+  if (c.arch == B2_ARCH_LERASUN) {
+    fprintf(stderr, "b2serve: random-init weights are built for the HF families; a Lerasun model directory needs its model.safetensors\n");
+    return -22;
+  }
   struct T { std::string name; size_t n; bool norm; };
   std::vector<T> ts;
   const size_t q = (size_t)c.num_q_heads * c.head_dim, kv = (size_t)c.num_kv_heads * c.head_dim, H = c.hidden, I = c.intermediate;

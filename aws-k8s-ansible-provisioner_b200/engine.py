@@ -12,7 +12,7 @@ from dataclasses import dataclass
 import numpy as np
 
 from . import capi
-from .capi import B2Error, b2_config, b2_sampling, check, load_library
+from .capi import B2Error, b2_config, b2_layer_spec, b2_sampling, check, load_library
 
 KERNEL_CLASSES = ["embed", "norm", "gemm_qkv", "rope_kv", "attn_decode", "chain", "gemm_o", "gemm_gateup", "act",
                   "gemm_down", "lmhead", "misc"]
@@ -41,6 +41,17 @@ class EngineConfig:
     rotary_dim: int = 0          # 0 = head_dim
     max_positions: int = 0       # OPT: learned position table rows - 2 (0 = max_model_len)
     sliding_window: int = 0      # Phi-3: attend to the last N keys only (0 = all)
+    layers: list | None = None   # layer-list families (arch "lerasun"): the "layers" entries of the model's config.json
+    compute_f32: bool = False    # families with an fp32 path: operands, weights and cache in fp32
+    logit_scale: float = 0.0     # lm_head output multiplier (0 = 1)
+
+    @staticmethod
+    def lerasun(model_cfg: dict, **runtime) -> "EngineConfig":
+        """From the dict a Lerasun config.json holds (width, vocab, norm.eps, logit_scale, layers) plus runtime sizing."""
+        return EngineConfig(num_layers=len(model_cfg["layers"]), hidden=model_cfg["width"], vocab=model_cfg["vocab"],
+                            rms_eps=model_cfg["norm"]["eps"], logit_scale=model_cfg.get("logit_scale", 1.0), arch="lerasun",
+                            layers=model_cfg["layers"], tie_embeddings=False, num_q_heads=0, num_kv_heads=0, head_dim=0,
+                            intermediate=0, **runtime)
 
     def kv_bytes_per_token(self) -> int:
         return 2 * self.num_layers * self.num_kv_heads * self.head_dim * 2
@@ -79,7 +90,15 @@ class Engine:
         c.rms_eps = cfg.rms_eps
         c.rope_theta = cfg.rope_theta
         c.gpu_mem_fraction = cfg.gpu_mem_fraction
-        c.arch = {"qwen3": capi.ARCH_QWEN3, "phi3": capi.ARCH_PHI3, "opt": capi.ARCH_OPT}[cfg.arch]
+        c.arch = {"qwen3": capi.ARCH_QWEN3, "phi3": capi.ARCH_PHI3, "opt": capi.ARCH_OPT, "lerasun": capi.ARCH_LERASUN}[cfg.arch]
+        c.compute_f32 = int(cfg.compute_f32)
+        c.logit_scale = float(cfg.logit_scale)
+        self._specs = None
+        if cfg.layers is not None:
+            self._specs = (b2_layer_spec * len(cfg.layers))()
+            for sp, layer in zip(self._specs, cfg.layers):
+                _fill_layer_spec(sp, layer)
+            c.layer_specs = self._specs
         c.rotary_dim = int(cfg.rotary_dim)
         c.max_positions = int(cfg.max_positions)
         c.sliding_window = int(cfg.sliding_window)
@@ -93,6 +112,27 @@ class Engine:
         check(self.lib.b2_engine_create(C.byref(c), path, device, C.byref(h)), self.lib)
         self.h = h
         self.device = device
+
+    @classmethod
+    def from_model_dir(cls, model_dir: str, device: int = 0, dtype: str = "bfloat16", **runtime) -> "Engine":
+        """The engine for the model a directory holds: the library's registry reads config.json and picks the family,
+        model.safetensors supplies the weights.  runtime: max_model_len, num_blocks, max_seqs, max_batch_tokens, ..."""
+        import os
+
+        lib = load_library()
+        c = b2_config()
+        specs = (b2_layer_spec * 1024)()
+        check(lib.b2_config_from_dir(model_dir.encode(), C.byref(c), specs, 1024), lib)
+        arch = {capi.ARCH_QWEN3: "qwen3", capi.ARCH_PHI3: "phi3", capi.ARCH_OPT: "opt", capi.ARCH_LERASUN: "lerasun"}[c.arch]
+        layers = None
+        if arch == "lerasun":
+            layers = [_layer_dict(specs[i]) for i in range(c.num_layers)]
+        cfg = EngineConfig(num_layers=c.num_layers, hidden=c.hidden, num_q_heads=c.num_q_heads, num_kv_heads=c.num_kv_heads,
+                           head_dim=c.head_dim, intermediate=c.intermediate, vocab=c.vocab, tie_embeddings=bool(c.tie_embeddings),
+                           rms_eps=c.rms_eps, rope_theta=c.rope_theta, arch=arch, rotary_dim=c.rotary_dim,
+                           max_positions=c.max_positions, sliding_window=c.sliding_window, layers=layers,
+                           compute_f32=(dtype == "float32"), logit_scale=c.logit_scale, **runtime)
+        return cls(cfg, device=device, safetensors_path=os.path.join(model_dir, "model.safetensors"))
 
     # ---- weights -----------------------------------------------------------------------
     def load_safetensors(self, paths) -> None:
@@ -118,6 +158,10 @@ class Engine:
         check(self.lib.b2_seq_create(self.h, int(reserve_tokens), C.byref(sid)), self.lib)
         return sid.value
 
+    def seq_reserve(self, seq_id: int, total_tokens: int) -> None:
+        """Grows a live sequence's page reservation to total_tokens."""
+        check(self.lib.b2_seq_reserve(self.h, int(seq_id), int(total_tokens)), self.lib)
+
     def seq_free(self, seq_id: int) -> None:
         check(self.lib.b2_seq_free(self.h, int(seq_id)), self.lib)
 
@@ -141,6 +185,18 @@ class Engine:
         out = np.zeros(len(prompts), dtype=np.int32)
         check(self.lib.b2_prefill(self.h, _p32(ids), _p32(offs), len(prompts), _p32(sids), _p32(out)), self.lib)
         return out
+
+    def prefill_logits(self, seq_ids, chunks, rows):
+        """Appends chunks[i] to sequence seq_ids[i] (a prompt portion, or one decoded token) in ONE forward and returns
+        (fp32 logits [len(rows)][vocab] at the given rows of the packed tokens, greedy next token per sequence)."""
+        ids = _i32(np.concatenate([np.asarray(p, dtype=np.int32) for p in chunks]))
+        offs = _i32(np.cumsum([0] + [len(p) for p in chunks]))
+        sids, r = _i32(seq_ids), _i32(rows)
+        out = np.zeros(len(chunks), dtype=np.int32)
+        logits = np.zeros((len(r), self.cfg.vocab), dtype=np.float32)
+        check(self.lib.b2_prefill_logits(self.h, _p32(ids), _p32(offs), len(chunks), _p32(sids), _p32(r), len(r),
+                                         logits.ctypes.data_as(C.POINTER(C.c_float)), _p32(out)), self.lib)
+        return logits, out
 
     def decode_step(self, seq_ids, in_tokens=None, want_output: bool = True):
         sids = _i32(seq_ids)
@@ -209,6 +265,12 @@ class Engine:
         check(self.lib.b2_get_hidden(self.h, layer, ntokens, out.ctypes.data_as(C.POINTER(C.c_uint16))), self.lib)
         return out
 
+    def get_hidden_f32(self, layer: int, ntokens: int) -> np.ndarray:
+        """Residual stream after `layer` (-1 = the normed embeddings) of the last forward, families with an fp32 stream."""
+        out = np.zeros((ntokens, self.cfg.hidden), dtype=np.float32)
+        check(self.lib.b2_get_hidden_f32(self.h, layer, ntokens, out.ctypes.data_as(C.POINTER(C.c_float))), self.lib)
+        return out
+
     def sample(self, nseq: int, temperature: float = 1.0, top_k: int = 0, top_p: float = 1.0, seed: int = 0) -> np.ndarray:
         p = b2_sampling(temperature, top_k, top_p, seed)
         out = np.zeros(nseq, dtype=np.int32)
@@ -236,6 +298,39 @@ class Engine:
 
     def __exit__(self, *a):
         self.close()
+
+
+def _fill_layer_spec(sp, layer: dict) -> None:
+    """One "layers" entry of a Lerasun config.json -> b2_layer_spec (the C registry does the same for a directory)."""
+    if layer["type"] != "latent_attention":
+        raise B2Error("mixer type %r not built" % layer["type"])
+    m = layer["mixer"]
+    sp.mixer = capi.MIXER_LATENT_ATTENTION
+    for k in ("heads", "dim", "rot_dim", "vdim", "kv_rank"):
+        setattr(sp, k, int(m[k]))
+    sp.kv_from = int(m["kv_from"]) if m.get("kv_from") is not None else -1
+    sp.rot_dims, sp.rot_base, sp.scale = int(m["rot"]["dims"]), float(m["rot"]["base"]), float(m["scale"])
+    mlp = layer.get("mlp")
+    sp.ff = capi.FF_NONE
+    if mlp is not None:
+        if mlp["kind"] != "moe":
+            raise B2Error("feed-forward kind %r not built" % mlp["kind"])
+        r = mlp["router"]
+        g = r.get("groups") or {"count": 1, "keep": 1}
+        sp.ff, sp.ff_dim, sp.experts, sp.top = capi.FF_ROUTED_EXPERTS, int(mlp["expert"]["ff"]), int(r["experts"]), int(r["top"])
+        sp.groups, sp.groups_keep = int(g["count"]), int(g["keep"])
+
+
+def _layer_dict(sp) -> dict:
+    m = {"heads": sp.heads, "dim": sp.dim, "rot_dim": sp.rot_dim, "vdim": sp.vdim, "kv_rank": sp.kv_rank, "scale": sp.scale,
+         "rot": {"base": sp.rot_base, "dims": sp.rot_dims}}
+    if sp.kv_from >= 0:
+        m["kv_from"] = sp.kv_from
+    mlp = None
+    if sp.ff == capi.FF_ROUTED_EXPERTS:
+        mlp = {"kind": "moe", "expert": {"ff": sp.ff_dim},
+               "router": {"experts": sp.experts, "top": sp.top, "groups": {"count": sp.groups, "keep": sp.groups_keep}}}
+    return {"type": "latent_attention", "mixer": m, "mlp": mlp}
 
 
 def bf16_bits_to_f32(bits: np.ndarray) -> np.ndarray:

@@ -25,9 +25,33 @@
 extern "C" {
 #endif
 
-#define B2_ABI_VERSION 2
+#define B2_ABI_VERSION 3
 
 typedef struct b2_engine b2_engine;
+
+/* One entry of a model whose layers are listed one by one (b2_config.layer_specs): which mixer the layer has, the
+ * mixer's sizes and constants, and its feed-forward.  Families whose layers are all alike (Qwen3, Phi-3, OPT) leave
+ * the list NULL and describe the layer through the scalar fields of b2_config. */
+enum b2_mixer_kind { B2_MIXER_LATENT_ATTENTION = 1 };
+enum b2_ff_kind { B2_FF_NONE = 0, B2_FF_ROUTED_EXPERTS = 1 };
+typedef struct b2_layer_spec {
+  int32_t mixer;        /* b2_mixer_kind */
+  int32_t heads;        /* query heads */
+  int32_t dim;          /* per head: query/key dims that are NOT rotated */
+  int32_t rot_dim;      /* per head: rotated query dims; the rotated key piece (one per token, shared by the heads) is as wide */
+  int32_t vdim;         /* per head: value dims */
+  int32_t kv_rank;      /* width of the per-token latent the keys and values are rebuilt from */
+  int32_t kv_from;      /* -1: the layer projects and stores its own latent; j >= 0: it reads what layer j stored */
+  int32_t rot_dims;     /* rotary positions turn the first rot_dims entries of the rotated piece, pairs (2i, 2i+1) */
+  float   rot_base;     /* angle of pair i at position p: p * rot_base^(-2i/rot_dims) */
+  float   scale;        /* softmax scale of the scores */
+  int32_t ff;           /* b2_ff_kind */
+  int32_t ff_dim;       /* inner width of one expert */
+  int32_t experts;      /* experts per layer */
+  int32_t top;          /* experts used per token */
+  int32_t groups;       /* experts form `groups` equal groups of neighbours ... */
+  int32_t groups_keep;  /* ... of which the best groups_keep may supply experts */
+} b2_layer_spec;
 
 /* Architecture + runtime sizing.  Field meanings follow HF Qwen3Config
  * (HF:models/qwen3/configuration_qwen3.py) and `vllm serve` flags the llm-d chart passes
@@ -57,6 +81,11 @@ typedef struct b2_config {
   int32_t rotary_dim;        /* width of the rotated prefix of each head; 0 = head_dim */
   int32_t max_positions;     /* OPT: rows of the learned position table minus 2; 0 = max_model_len */
   int32_t sliding_window;    /* Phi-3: every query attends to its last `sliding_window` keys only; 0 = all */
+  /* ABI 3 */
+  const b2_layer_spec* layer_specs; /* [num_layers] for families with a layer list (Lerasun), else NULL; copied by b2_engine_create */
+  int32_t compute_f32;       /* 1: activations, weights and cache in fp32, every product in true fp32 (families that have such a
+                                path: Lerasun); 0: bf16 operands with fp32 accumulation */
+  float   logit_scale;       /* the lm_head's output is multiplied by this (0 = 1) */
 } b2_config;
 
 /* Model families.  QWEN3: HF:models/qwen3/modeling_qwen3.py (QK-norm, separate q/k/v and gate/up
@@ -68,7 +97,20 @@ typedef struct b2_config {
  * fc1/fc2 projections, query pre-scaled by head_dim^-0.5, ReLU, tied lm_head; rms_eps carries the
  * LayerNorm eps; the do_layer_norm_before=False (350m) and word_embed_proj_dim != hidden variants are
  * not built). */
-enum b2_arch { B2_ARCH_QWEN3 = 0, B2_ARCH_PHI3 = 1, B2_ARCH_OPT = 2 };
+/* LERASUN: a layer list (b2_config.layer_specs).  Every layer adds a mixer branch and a feed-forward branch, both computed
+ * from the same residual stream through two unit-offset RMS norms, back onto an fp32 residual stream; mixers are
+ * latent attention (one shared low-rank latent + one rotated key piece per token, a per-head softmax sink, optional reuse of
+ * an earlier layer's cache), feed-forwards are routed squared-ReLU experts.  Tensor names: embed, embed.norm,
+ * l<i>.norm1|norm2, l<i>.mix.{q,dkv,dkv.norm,uk,uv,sink,o}, l<i>.mlp.{e<k>.up,e<k>.down,router,correction}, final.norm, head.
+ * hidden = width; num_q_heads, head_dim, intermediate are unused. */
+enum b2_arch { B2_ARCH_QWEN3 = 0, B2_ARCH_PHI3 = 1, B2_ARCH_OPT = 2, B2_ARCH_LERASUN = 3 };
+
+/* Model registry: reads MODEL_DIR/config.json and fills the architecture fields of *cfg (the runtime sizing fields --
+ * max_model_len, block_size, num_blocks, max_seqs, max_batch_tokens, use_cuda_graphs, compute_f32 -- are left as the caller
+ * set them).  HF configs are told apart by "model_type" (qwen3, phi3, opt); a config with "architecture": "Lerasun" fills
+ * specs[0 .. num_layers) as well and points cfg->layer_specs at it (max_specs = capacity of specs; may be 0 / NULL for the
+ * HF families).  Returns 0, or a negative code with b2_last_error(). */
+int  b2_config_from_dir(const char* model_dir, b2_config* cfg, b2_layer_spec* specs, int32_t max_specs);
 
 const char* b2_last_error(void);
 int  b2_abi_version(void);
@@ -91,6 +133,9 @@ int  b2_engine_info(b2_engine* e, int64_t* num_blocks, int64_t* free_blocks, int
 /* ---- sequences (paged KV allocator; HF:...modeling_qwen3.py:270-271 cache update) ------- */
 /* Reserves pages for up to reserve_tokens tokens (prompt + output) and returns a slot id. */
 int  b2_seq_create(b2_engine* e, int32_t reserve_tokens, int32_t* seq_id);
+/* Grows the reservation of a live sequence to total_tokens (no-op when it already holds that many): a scheduler that does
+ * not know a request's final length takes pages as the tokens arrive.  Fails with -12 when the pool has no pages left. */
+int  b2_seq_reserve(b2_engine* e, int32_t seq_id, int32_t total_tokens);
 int  b2_seq_free(b2_engine* e, int32_t seq_id);
 int  b2_seq_len(b2_engine* e, int32_t seq_id);
 /* Drops the tail of a sequence (new_len <= current length); its pages stay reserved.  Used to
@@ -117,6 +162,13 @@ int  b2_decode_step(b2_engine* e, int32_t nseq, const int32_t* seq_ids, const in
 int  b2_decode_run(b2_engine* e, int32_t nseq, const int32_t* seq_ids, int32_t steps,
                    int32_t* out_tokens, float* elapsed_ms);
 
+/* Like b2_prefill, for callers that want logits at chosen places instead of a next token per sequence: rows[0 .. nrows)
+ * index the call's tokens in the order given (0 = first token of the first sequence), out_logits (host) receives
+ * [nrows][vocab] fp32.  nrows may be 0.  A sequence may bring a single token (a decode step run beside other sequences'
+ * prompt portions).  Greedy next tokens are still produced for every sequence's last position. */
+int  b2_prefill_logits(b2_engine* e, const int32_t* ids, const int32_t* seq_offsets, int32_t nseq, const int32_t* seq_ids,
+                       const int32_t* rows, int32_t nrows, float* out_logits, int32_t* out_tokens);
+
 /* Logits of the last forward's last positions, [nseq][vocab] fp32 on the host. */
 int  b2_get_logits(b2_engine* e, int32_t nseq, float* out_logits);
 /* Residual stream after layer `layer` (0-based; -1 = embeddings, num_layers = final norm
@@ -124,6 +176,8 @@ int  b2_get_logits(b2_engine* e, int32_t nseq, float* out_logits);
  * Only filled when debug capture was enabled with b2_set_debug(e, 1). */
 int  b2_set_debug(b2_engine* e, int32_t capture_hidden);
 int  b2_get_hidden(b2_engine* e, int32_t layer, int32_t ntokens, uint16_t* out_bf16);
+/* The same for families whose residual stream is fp32 (Lerasun): [ntokens][hidden] floats. */
+int  b2_get_hidden_f32(b2_engine* e, int32_t layer, int32_t ntokens, float* out_f32);
 
 /* Measurement knobs that can change while the engine lives (bench.py's ablation leg, the two-lane tests); every
  * call drops the captured decode graphs, so the next step re-captures with the new setting.
