@@ -14,6 +14,13 @@
 // Tile 64 x 64 x 16, 256 threads, 4 x 4 outputs per thread, operands staged in shared memory as fp32; every global
 // access is bounds-checked, so no size needs padding.  Rows of one output are summed in k order by one thread: the
 // result of a row does not depend on which other rows share its tile.
+//
+// bf16 operands take the tensor-core form of the same tile (gemm_any_mma_kernel: warp-level 16 x 16 x 16 bf16 MMAs with
+// fp32 accumulators, four warps of 32 x 32 outputs, 64 x 32 operand slabs staged with 16-byte loads when rows are
+// 16-byte aligned and element by element when they are not); the fp32 form stays on plain FMAs because a true-fp32
+// product has no tensor-core mode.  Same grid, same epilogues, same independence of a row from its tile mates.
+#include <mma.h>
+
 #include "kernels.h"
 
 namespace b2 {
@@ -109,6 +116,116 @@ __global__ void __launch_bounds__(256) gemm_any_kernel(AnyGemm g) {
   }
 }
 
+constexpr int MK = 32, MLD = MK + 8;  // k-slab of the MMA form and its padded row stride in shared memory (elements)
+
+template <typename TC>
+__global__ void __launch_bounds__(128) gemm_any_mma_kernel(AnyGemm g) {
+  using namespace nvcuda;
+  __shared__ __align__(32) unsigned char smem_raw[BM * (BN + 4) * 4];  // operand slabs during the k loop, the fp32 tile afterwards
+  bf16* As = reinterpret_cast<bf16*>(smem_raw);                         // [BM][MLD]
+  bf16* Ws = As + BM * MLD;                                             // [BN][MLD]
+  float* Cs = reinterpret_cast<float*>(smem_raw);                       // [BM][BN + 4]
+  __shared__ long a_rows_s[BM];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const bf16* A = reinterpret_cast<const bf16*>(g.A);
+  const bf16* W = reinterpret_cast<const bf16*>(g.W);
+  TC* C = reinterpret_cast<TC*>(g.C);
+  int row0, row_end;
+  if (g.tile_group != nullptr) {
+    if ((int)blockIdx.x >= *g.n_tiles) return;
+    const int grp = g.tile_group[blockIdx.x];
+    row0 = g.tile_row0[blockIdx.x];
+    row_end = min(row0 + BM, g.group_offsets[grp + 1]);
+    W += (size_t)grp * g.w_bs;
+  } else {
+    row0 = blockIdx.x * BM;
+    row_end = min(row0 + BM, g.M);
+    A += (size_t)blockIdx.z * g.a_bs;
+    W += (size_t)blockIdx.z * g.w_bs;
+    C += (size_t)blockIdx.z * g.c_bs;
+  }
+  const int n0 = blockIdx.y * BN;
+  if (tid < BM) a_rows_s[tid] = (row0 + tid < row_end) ? (g.a_rows ? (long)g.a_rows[row0 + tid] : (long)(row0 + tid)) : -1;
+  __syncthreads();
+  // 16-byte loads need every row start and every k offset on a 16-byte boundary
+  const bool a_vec = (g.lda % 8 == 0) && ((reinterpret_cast<uintptr_t>(A) & 15) == 0);
+  const bool w_vec = (g.ldw % 8 == 0) && ((reinterpret_cast<uintptr_t>(W) & 15) == 0);
+  wmma::fragment<wmma::accumulator, 16, 16, 16, float> acc[2][2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int j = 0; j < 2; ++j) wmma::fill_fragment(acc[i][j], 0.f);
+  const int wm = (warp >> 1) * 32, wn = (warp & 1) * 32;
+  for (int k0 = 0; k0 < g.K; k0 += MK) {
+    // stage: 64 rows x 32 k of each operand = 256 chunks of 8 elements; two chunks per thread and operand
+#pragma unroll
+    for (int it = 0; it < 2; ++it) {
+      const int ch = tid + it * 128, r = ch >> 2, kc = (ch & 3) * 8, k = k0 + kc;
+      uint4 va = make_uint4(0, 0, 0, 0), vw = make_uint4(0, 0, 0, 0);
+      const long ar = a_rows_s[r];
+      if (ar >= 0) {
+        const bf16* src = A + ar * g.lda + k;
+        if (a_vec && k + 8 <= g.K) va = *reinterpret_cast<const uint4*>(src);
+        else {
+          bf16* e = reinterpret_cast<bf16*>(&va);
+          for (int j = 0; j < 8; ++j)
+            if (k + j < g.K) e[j] = src[j];
+        }
+      }
+      if (n0 + r < g.N) {
+        const bf16* src = W + (long)(n0 + r) * g.ldw + k;
+        if (w_vec && k + 8 <= g.K) vw = ld_stream(src);
+        else {
+          bf16* e = reinterpret_cast<bf16*>(&vw);
+          for (int j = 0; j < 8; ++j)
+            if (k + j < g.K) e[j] = src[j];
+        }
+      }
+      *reinterpret_cast<uint4*>(As + r * MLD + kc) = va;
+      *reinterpret_cast<uint4*>(Ws + r * MLD + kc) = vw;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < MK; kk += 16) {
+      wmma::fragment<wmma::matrix_a, 16, 16, 16, bf16, wmma::row_major> fa[2];
+      wmma::fragment<wmma::matrix_b, 16, 16, 16, bf16, wmma::col_major> fb[2];
+#pragma unroll
+      for (int i = 0; i < 2; ++i) wmma::load_matrix_sync(fa[i], As + (wm + 16 * i) * MLD + kk, MLD);
+#pragma unroll
+      for (int j = 0; j < 2; ++j) wmma::load_matrix_sync(fb[j], Ws + (wn + 16 * j) * MLD + kk, MLD);
+#pragma unroll
+      for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 2; ++j) wmma::mma_sync(acc[i][j], fa[i], fb[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int j = 0; j < 2; ++j) wmma::store_matrix_sync(Cs + (wm + 16 * i) * (BN + 4) + wn + 16 * j, acc[i][j], BN + 4, wmma::mem_row_major);
+  __syncthreads();
+  for (int idx = tid; idx < BM * BN; idx += 128) {
+    const int rr = idx / BN, cc = idx - rr * BN;
+    const int r = row0 + rr, n = n0 + cc;
+    if (r >= row_end || n >= g.N) continue;
+    float v = Cs[rr * (BN + 4) + cc] * g.alpha;
+    TC* dst = C + (size_t)r * g.ldc + n;
+    if (g.epilogue == ANY_EPI_RELU2) {
+      v = fmaxf(v, 0.f);
+      v = v * v;
+    }
+    if (g.epilogue == ANY_EPI_ADD) {
+      if constexpr (sizeof(TC) == 4) *dst = (TC)((float)*dst + v);
+    } else {
+      if constexpr (sizeof(TC) == 4) *dst = v;
+      else *dst = __float2bfloat16_rn(v);
+    }
+  }
+}
+
 // One CTA: tiles of the ragged groups.  group_offsets [G + 1] -> (tile_group, tile_row0, n_tiles).
 __global__ void ragged_tiles_kernel(const int* __restrict__ group_offsets, int G, int* __restrict__ tile_group, int* __restrict__ tile_row0,
                                     int* __restrict__ n_tiles, int cap) {
@@ -145,8 +262,11 @@ int launch_gemm_any(const AnyGemm& g, int a_f32, int w_f32, int c_f32, int batch
     if (g.M <= 0) return 0;
     grid = dim3((g.M + BM - 1) / BM, (g.N + BN - 1) / BN, batch > 0 ? batch : 1);
   }
+  static const bool use_mma = [] { const char* e = getenv("B2_ANY_MMA"); return !(e && *e == '0'); }();  // 0: bf16 operands on plain FMAs too (cross-check)
 #define GA(TA, TW, TC) B2_CUDA_OK(b2_launch(gemm_any_kernel<TA, TW, TC>, grid, dim3(256), 0, s, g))
   if (a_f32 && w_f32 && c_f32) GA(float, float, float);
+  else if (!a_f32 && !w_f32 && use_mma && c_f32) B2_CUDA_OK(b2_launch(gemm_any_mma_kernel<float>, grid, dim3(128), 0, s, g));
+  else if (!a_f32 && !w_f32 && use_mma && !c_f32) B2_CUDA_OK(b2_launch(gemm_any_mma_kernel<bf16>, grid, dim3(128), 0, s, g));
   else if (!a_f32 && !w_f32 && c_f32) GA(bf16, bf16, float);
   else if (!a_f32 && !w_f32 && !c_f32) GA(bf16, bf16, bf16);
   else if (a_f32 && !w_f32 && c_f32) GA(float, bf16, float);

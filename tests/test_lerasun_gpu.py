@@ -1,0 +1,321 @@
+"""The Lerasun family through the engine (GPU) against the plain restatement in oracle/lerasun_oracle.py.
+
+Every test builds its own small configuration and random weights.  The engine runs in fp32 (tight bars: a lost key, a
+window one token off, a stale page or a missing sink shows far above fp32 rounding) and in bf16 (loose bars).
+What is covered: every layer's residual stream; whole prompts against token-by-token decoding; prompt portions down to two
+tokens; unequal requests in one batch against each alone; pages and sequence slots that are freed and used again; keys far
+back and at page borders with sharpened attention; the first tokens of a sequence; a long run of decode steps; sizes that
+differ per layer, group selection that actually drops groups, layers without a feed-forward, layers that read another
+layer's cache; greedy generation through the engine's own prefill / decode entry points and through b2serve's scheduler.
+"""
+import http.client
+import json
+import os
+import subprocess
+import time
+
+import numpy as np
+import pytest
+import torch
+
+from _util import pkg
+from oracle.lerasun_oracle import Oracle, random_weights
+
+pytestmark = pytest.mark.gpu
+
+
+def mixer(heads, dim, rot, vdim, rank, scale, base=10000.0, kv_from=None):
+    m = {"heads": heads, "dim": dim, "rot_dim": rot, "vdim": vdim, "kv_rank": rank, "scale": scale, "rot": {"base": base, "dims": rot}}
+    if kv_from is not None:
+        m["kv_from"] = kv_from
+    return m
+
+
+def moe(ff, experts, top, groups, keep):
+    return {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": experts, "top": top, "groups": {"count": groups, "keep": keep}}}
+
+
+def layer(m, mlp):
+    return {"type": "latent_attention", "mixer": m, "mlp": mlp}
+
+
+def cfg_a():
+    """Odd sizes, none a multiple of a tile; groups that are dropped; a layer with no feed-forward; two cache readers."""
+    return {"architecture": "Lerasun", "vocab": 203, "width": 88, "logit_scale": 0.5, "norm": {"eps": 1e-5}, "layers": [
+        layer(mixer(3, 12, 6, 20, 40, 0.3), moe(36, 6, 3, 3, 2)),
+        layer(mixer(3, 12, 6, 20, 40, 0.3, kv_from=0), moe(36, 6, 3, 3, 2)),
+        layer(mixer(5, 8, 10, 6, 24, 0.21, base=500.0), None),
+        layer(mixer(2, 20, 10, 14, 24, 0.4, base=500.0, kv_from=2), moe(20, 8, 2, 4, 1)),
+    ]}
+
+
+def cfg_b():
+    """One group, every expert used (top == experts), one head, latent wider than 32 lanes x 1."""
+    return {"architecture": "Lerasun", "vocab": 97, "width": 64, "logit_scale": 1.0, "norm": {"eps": 1e-6}, "layers": [
+        layer(mixer(1, 16, 4, 16, 72, 0.25), moe(24, 2, 2, 1, 1)),
+        layer(mixer(4, 4, 2, 8, 16, 0.5, base=100.0), moe(8, 4, 1, 2, 2)),
+    ]}
+
+
+def sharpen(w, cfg, factor=6.0):
+    """Scaled queries make every softmax peak on a few keys, wherever they are: a key that is lost shows."""
+    for i, _ in enumerate(cfg["layers"]):
+        w[f"l{i}.mix.q"] = (w[f"l{i}.mix.q"] * factor).to(torch.bfloat16).float()
+    return w
+
+
+def engine(cfg, w, f32=True, **rt):
+    P = pkg()
+    rt = {"max_model_len": 1024, "num_blocks": 80, "max_seqs": 4, "max_batch_tokens": 1024, **rt}
+    e = P.Engine(P.EngineConfig.lerasun(cfg, compute_f32=f32, **rt))
+    e.load_state_dict({k: v.to(torch.bfloat16) for k, v in w.items()})
+    return e
+
+
+def tokens(cfg, n, seed):
+    return torch.randint(0, cfg["vocab"], (n,), generator=torch.Generator().manual_seed(seed)).tolist()
+
+
+def err(got, ref):
+    got, ref = np.asarray(got, dtype=np.float64), np.asarray(ref, dtype=np.float64)
+    return float(np.abs(got - ref).max() / max(np.abs(ref).max(), 1e-9))
+
+
+F32_BAR, BF16_BAR = 2e-5, 6e-2
+
+
+@pytest.mark.parametrize("make", [cfg_a, cfg_b])
+def test_every_layer_fp32(make):
+    cfg = make()
+    w = random_weights(cfg, seed=1)
+    toks = tokens(cfg, 37, 2)
+    ref_logits, ref_layers = Oracle(cfg, w).forward(toks, capture_layers=True)
+    with engine(cfg, w) as e:
+        e.set_debug(hidden=True)
+        sid = e.seq_create(64)
+        logits, _ = e.prefill_logits([sid], [toks], list(range(len(toks))))
+        for l in range(len(cfg["layers"])):
+            assert err(e.get_hidden_f32(l, len(toks)), ref_layers[l].numpy()) < F32_BAR, "residual stream after layer %d" % l
+        assert err(logits, ref_logits.numpy()) < F32_BAR
+
+
+@pytest.mark.parametrize("make", [cfg_a, cfg_b])
+def test_bf16_close_to_oracle(make):
+    cfg = make()
+    w = random_weights(cfg, seed=3)
+    toks = tokens(cfg, 50, 4)
+    ref = Oracle(cfg, w).forward(toks).numpy()
+    with engine(cfg, w, f32=False) as e:
+        sid = e.seq_create(64)
+        logits, _ = e.prefill_logits([sid], [toks[:41]], list(range(41)))
+        assert err(logits, ref[:41]) < BF16_BAR
+        for p in range(41, 50):
+            e.decode_step([sid], in_tokens=[toks[p]], want_output=False)
+            assert err(e.get_logits(1)[0], ref[p]) < BF16_BAR
+
+
+def test_prefill_against_token_by_token_decoding():
+    cfg = cfg_a()
+    w = sharpen(random_weights(cfg, seed=5), cfg)
+    toks = tokens(cfg, 70, 6)
+    ref = Oracle(cfg, w).forward(toks).numpy()
+    with engine(cfg, w) as e:
+        whole = e.seq_create(80)
+        lw, _ = e.prefill_logits([whole], [toks], list(range(70)))
+        assert err(lw, ref) < F32_BAR
+        one = e.seq_create(80)     # the first token as a one-token prompt, everything after it as decode steps
+        l0, _ = e.prefill_logits([one], [toks[:1]], [0])
+        assert err(l0[0], ref[0]) < F32_BAR
+        for p in range(1, 70):
+            e.decode_step([one], in_tokens=[toks[p]], want_output=False)
+            got = e.get_logits(1)[0]
+            assert err(got, ref[p]) < F32_BAR, "decoded position %d" % p
+            assert err(got, lw[p]) < F32_BAR
+
+
+@pytest.mark.parametrize("cuts", [[2, 2, 2, 64, 3, 17, 2, 31], [16, 16, 32, 1, 1, 57], [63, 2, 58]])
+def test_portions_of_a_prompt(cuts):
+    cfg = cfg_a()
+    w = sharpen(random_weights(cfg, seed=7), cfg)
+    n = sum(cuts)
+    toks = tokens(cfg, n, 8)
+    ref = Oracle(cfg, w).forward(toks).numpy()
+    with engine(cfg, w) as e:
+        sid = e.seq_create(n)
+        at = 0
+        for c in cuts:
+            lg, _ = e.prefill_logits([sid], [toks[at:at + c]], list(range(c)))
+            assert err(lg, ref[at:at + c]) < F32_BAR, "portion at %d of %d tokens" % (at, c)
+            at += c
+
+
+def test_mixed_batch_equals_each_alone():
+    cfg = cfg_a()
+    w = sharpen(random_weights(cfg, seed=9), cfg)
+    lens = [140, 5, 60, 1]
+    prompts = [tokens(cfg, n, 20 + i) for i, n in enumerate(lens)]
+    refs = [Oracle(cfg, w).forward(p).numpy() for p in prompts]
+    with engine(cfg, w) as e:
+        sids = [e.seq_create(160) for _ in prompts]
+        done = [0, 0, 0, 0]
+        # unequal portions beside single tokens, several steps; request 3 is one token long and joins late
+        plan = [[(0, 64), (1, 3)], [(0, 2), (1, 1), (2, 40)], [(0, 60), (1, 1), (2, 1), (3, 1)], [(0, 4), (2, 6)]]
+        for step in plan:
+            chunks, rows, base = [], [], 0
+            for r, c in step:
+                chunks.append(prompts[r][done[r]:done[r] + c])
+                rows += list(range(base, base + c))
+                base += c
+            lg, _ = e.prefill_logits([sids[r] for r, _ in step], chunks, rows)
+            base = 0
+            for r, c in step:
+                assert err(lg[base:base + c], refs[r][done[r]:done[r] + c]) < F32_BAR, "request %d at %d" % (r, done[r])
+                base += c
+                done[r] += c
+        # a pure decode batch of unequal lengths (the captured step), against the same references
+        live = [0, 2]
+        e.decode_step([sids[r] for r in live], in_tokens=[prompts[r][done[r]] for r in live], want_output=False)
+        lg = e.get_logits(2)
+        for k, r in enumerate(live):
+            assert err(lg[k], refs[r][done[r]]) < F32_BAR
+
+
+def test_pages_and_slots_are_used_again():
+    cfg = cfg_b()
+    w = sharpen(random_weights(cfg, seed=11), cfg)
+    with engine(cfg, w, num_blocks=9, max_seqs=2, max_model_len=128, max_batch_tokens=128) as e:   # 8 usable pages = 128 tokens
+        for rnd in range(5):
+            n = [100, 28][rnd % 2] if rnd < 4 else 120
+            toks = tokens(cfg, n, 30 + rnd)
+            ref = Oracle(cfg, w).forward(toks).numpy()
+            sid = e.seq_create(16)
+            other = e.seq_create(8) if rnd % 2 else None   # a second live request takes pages in between
+            at = 0
+            for c in [16, n - 16 - 4, 1, 1, 1, 1]:
+                e.seq_reserve(sid, at + c)
+                lg, _ = e.prefill_logits([sid], [toks[at:at + c]], list(range(c)))
+                assert err(lg, ref[at:at + c]) < F32_BAR, "round %d at %d" % (rnd, at)
+                at += c
+            e.seq_free(sid)
+            if other is not None:
+                e.seq_free(other)
+        assert e.info()["free_blocks"] == 8
+
+
+def test_far_keys_and_page_borders():
+    """One token id occurs once, far back; every layer's queries are scaled up, so late positions lean on single keys."""
+    cfg = cfg_b()
+    w = sharpen(random_weights(cfg, seed=13), cfg, factor=10.0)
+    n = 600
+    toks = tokens(cfg, n, 14)
+    ref = Oracle(cfg, w).forward(toks).numpy()
+    want = [0, 1, 2, 15, 16, 17, 31, 32, 33, 255, 256, 257, 511, 512, 513, 598, 599]
+    with engine(cfg, w, num_blocks=100) as e:
+        sid = e.seq_create(n + 40)
+        lg, _ = e.prefill_logits([sid], [toks], want)
+        assert err(lg, ref[want]) < F32_BAR
+        # the same positions reached by decoding over page borders (positions 560..599 decoded one by one)
+        sid2 = e.seq_create(n + 40)
+        e.prefill_logits([sid2], [toks[:560]], [])
+        for p in range(560, n):
+            e.decode_step([sid2], in_tokens=[toks[p]], want_output=False)
+            if p in (575, 576, 577, 591, 592, 593, 599):
+                assert err(e.get_logits(1)[0], ref[p]) < F32_BAR, "decoded position %d" % p
+
+
+def test_sink_counts_once_and_has_no_value():
+    cfg = cfg_b()
+    w = random_weights(cfg, seed=15)
+    toks = tokens(cfg, 24, 16)
+    for sink in (-30.0, 0.0, 4.0, 30.0):
+        for i in range(len(cfg["layers"])):
+            w[f"l{i}.mix.sink"] = torch.full_like(w[f"l{i}.mix.sink"], sink)
+        ref = Oracle(cfg, w).forward(toks).numpy()
+        with engine(cfg, w) as e:
+            sid = e.seq_create(32)
+            lg, _ = e.prefill_logits([sid], [toks], list(range(24)))
+            assert err(lg, ref) < F32_BAR, "sink %g" % sink
+    # a sink that swallows the softmax leaves the feed-forward branch alone: the mixer adds (almost) nothing
+    w2 = {k: v.clone() for k, v in w.items()}
+    for i in range(len(cfg["layers"])):
+        w2[f"l{i}.mix.o"] = torch.zeros_like(w2[f"l{i}.mix.o"])
+    ref_no_mixer = Oracle(cfg, w2).forward(toks).numpy()
+    assert err(lg, ref_no_mixer) < 1e-6
+
+
+def test_long_decoding():
+    cfg = cfg_a()
+    w = sharpen(random_weights(cfg, seed=17), cfg)
+    n = 230
+    toks = tokens(cfg, n, 18)
+    ref = Oracle(cfg, w).forward(toks).numpy()
+    with engine(cfg, w) as e:
+        sid = e.seq_create(n)
+        e.prefill_logits([sid], [toks[:20]], [])
+        worst = 0.0
+        for p in range(20, n):
+            e.decode_step([sid], in_tokens=[toks[p]], want_output=False)
+            worst = max(worst, err(e.get_logits(1)[0], ref[p]))
+        assert worst < F32_BAR
+
+
+def test_greedy_generation_through_the_engine():
+    cfg = cfg_a()
+    w = random_weights(cfg, seed=19)
+    prompts = [tokens(cfg, 33, 40), tokens(cfg, 9, 41)]
+    refs = [Oracle(cfg, w).greedy(p, 12) for p in prompts]
+    with engine(cfg, w) as e:
+        sids = [e.seq_create(64) for _ in prompts]
+        out = [e.prefill(sids, prompts)]
+        for _ in range(11):
+            out.append(e.decode_step(sids))          # the token feedback stays on the device
+        got = np.stack(out, axis=1)
+        for i in range(2):
+            assert got[i].tolist() == refs[i], (got[i].tolist(), refs[i])
+
+
+def test_greedy_generation_through_the_server(tmp_path):
+    """b2serve picks the family from config.json, loads model.safetensors, and its scheduler (chunked prefill, then decode
+    steps over the running requests) generates what the oracle generates."""
+    P = pkg()
+    import importlib
+    weights = importlib.import_module("aws-k8s-ansible-provisioner_b200.weights")
+    exe = os.path.join(os.path.dirname(P.LIB_PATH), "b2serve")
+    assert os.path.exists(exe), "b2serve not built"
+    cfg = cfg_a()
+    cfg["vocab"] = 1000         # the byte tokenizer renders ids >= 256 as <|id|>: those are read back from the reply's text
+    w = random_weights(cfg, seed=21)
+    weights.write_safetensors({k: v.to(torch.bfloat16) for k, v in w.items()}, str(tmp_path / "model.safetensors"))
+    (tmp_path / "config.json").write_text(json.dumps(cfg))
+    proc = subprocess.Popen([exe, str(tmp_path), "--served-model-name", "lerasun-test", "--port", "0", "--host", "127.0.0.1", "--max-model-len", "256",
+                             "--max-num-seqs", "4", "--num-gpu-blocks-override", "64", "--max-num-batched-tokens", "32", "--eos-token-id", "-1",
+                             "--dtype", "float32"], stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)
+    try:
+        port, t0 = None, time.time()
+        while time.time() - t0 < 120:
+            line = proc.stdout.readline()
+            if line.startswith("READY"):
+                port = int(line.split()[1])
+                break
+            if proc.poll() is not None:
+                break
+        assert port is not None, "b2serve did not start: " + proc.stderr.read()
+        prompt = tokens(cfg, 70, 22)   # longer than --max-num-batched-tokens: prefilled in three portions
+        c = http.client.HTTPConnection("127.0.0.1", port, timeout=120)
+        c.request("POST", "/v1/completions", body=json.dumps({"model": "lerasun-test", "prompt": prompt, "max_tokens": 10, "temperature": 0,
+                                                              "ignore_eos": True}), headers={"Content-Type": "application/json"})
+        r = c.getresponse()
+        body = json.loads(r.read().decode())
+        assert r.status == 200, body
+        ref = Oracle(cfg, w).greedy(prompt, 10)
+        import re
+        got_big = [int(x) for x in re.findall(r"<\|(\d+)\|>", body["choices"][0]["text"])]
+        ref_big = [t for t in ref if t >= 256]
+        assert body["usage"]["completion_tokens"] == 10
+        assert len(ref_big) >= 5 and got_big == ref_big, (body["choices"][0]["text"], ref)
+    finally:
+        proc.terminate()
+        try:
+            proc.wait(timeout=10)
+        except Exception:
+            proc.kill()
