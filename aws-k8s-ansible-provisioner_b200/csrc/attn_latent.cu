@@ -13,10 +13,24 @@
 // the operands handed on are fp32 or bf16.  Kernels:
 //   latent_finish     what follows the fused q | latent projection: rotary on the query's rotated piece, unit-RMS norm of
 //                     the latent with a plain gain, rotary on the shared key piece, cache row write
-//   latent_attention  one warp per (query token, head); a CTA's eight rows share 32-key tiles staged in shared memory; lane j
+//   latent_attention_mma   bf16 cache: 64 (token, head) rows x 64-key tiles on warp-level bf16 MMAs with fp32 accumulators.  Two
+//                     sweeps over the keys: the first finds every row's maximum (Q.K^T only), the second forms
+//                     P = exp(s - max) and accumulates P.C with no rescaling in between, so the accumulators never
+//                     leave the MMA fragments.  The keys of a row block may be cut into splits that run as CTAs of their
+//                     own (decode steps: few rows, long caches); splits leave (max, sum, unnormalised sum of latents) and
+//                     latent_merge folds them, and the sink, into the output
+//   latent_attention  fp32 cache (and latents wider than 512): one warp per (query token, head); a CTA's eight rows share 32-key tiles staged in shared memory; lane j
 //                     scores key j, then lane d accumulates latent dims d, d + 32, ...; the same kernel serves prompt
 //                     portions (64-token tiles over the block table) and decode steps (one row per sequence)
+#include <mma.h>
+
 #include "kernels.h"
+
+#define B2_TRY_RC(expr)      \
+  do {                      \
+    int _r = (expr);        \
+    if (_r != 0) return _r; \
+  } while (0)
 
 namespace b2 {
 
@@ -204,6 +218,252 @@ __global__ void __launch_bounds__(LA_WARPS * 32) latent_attention_kernel(const f
   }
 }
 
+// ---- tensor-core form -----------------------------------------------------------------------------------------------
+constexpr int MA_ROWS = 64, MA_KEYS = 64, MA_THREADS = 256;
+
+struct MmaAttnArgs {
+  const float* q_abs;
+  const float* q_rot;
+  const bf16* cache;
+  LatentGeom g;
+  const int32_t* block_table;
+  int bt_stride, block_size;
+  const PrefillTile* tiles;
+  const int32_t* positions;
+  const int32_t* seq_lens;
+  const float* sink;
+  bf16* out_lat;
+  float* partial;   // nsplit > 1: [(token row * heads + head) * nsplit + split][kv_rank + 2] = max, sum, sum of p * latent
+  int nsplit;
+};
+
+// NF: 16-wide output column fragments per warp (8 warps): kv_rank <= 128 * NF
+template <int NF>
+__global__ void __launch_bounds__(MA_THREADS, 1) latent_attention_mma_kernel(MmaAttnArgs a) {
+  using namespace nvcuda;
+  extern __shared__ __align__(128) unsigned char smraw[];
+  pdl_wait();
+  pdl_launch_dependents();
+  const LatentGeom& g = a.g;
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int R = g.kv_rank, D = R + g.rot_dim, D16 = (D + 15) & ~15, DP = D16 + 8, R16 = (R + 15) & ~15;
+  bf16* Qs = reinterpret_cast<bf16*>(smraw);                 // [64][DP]
+  bf16* Ks = Qs + MA_ROWS * DP;                              // [64][DP]
+  float* Ss = reinterpret_cast<float*>(Ks + MA_KEYS * DP);   // [64][68]
+  bf16* Ps = reinterpret_cast<bf16*>(Ss + MA_ROWS * 68);     // [64][72]
+  float* row_m = reinterpret_cast<float*>(Ps + MA_ROWS * 72);  // [64]
+  float* row_l = row_m + MA_ROWS;                            // [64]
+  int* row_pos = reinterpret_cast<int*>(row_l + MA_ROWS);    // [64]
+  float* Os = reinterpret_cast<float*>(smraw);               // after the sweeps: [64][R16 + 4] over Qs / Ks
+
+  int q_row0, q_pos0, nrows, bt_row;
+  if (a.tiles != nullptr) {
+    const PrefillTile tl = a.tiles[blockIdx.x];
+    q_row0 = tl.q_row0; q_pos0 = tl.q_pos0; nrows = tl.nrows; bt_row = tl.bt_row;
+  } else {
+    q_row0 = blockIdx.x; q_pos0 = a.positions[blockIdx.x]; nrows = a.seq_lens[blockIdx.x] > 0 ? 1 : 0; bt_row = blockIdx.x;
+  }
+  const int total = nrows * g.heads;
+  const int first = blockIdx.y * MA_ROWS;
+  if (first >= total) return;
+  const int split = blockIdx.z;
+  const int last_row = min(first + MA_ROWS, total) - 1;
+  const int max_pos = q_pos0 + last_row / g.heads;
+  // this split's keys: whole 64-key tiles [t_lo, t_hi)
+  const int ntile = max_pos / MA_KEYS + 1;
+  const int per = (ntile + a.nsplit - 1) / a.nsplit;
+  const int t_lo = split * per, t_hi = min(ntile, t_lo + per);
+
+  // ---- stage Q (bf16), zero the padding columns of both operand slabs ----
+  for (int idx = tid; idx < MA_ROWS * DP; idx += MA_THREADS) {
+    const int r = idx / DP, d = idx - r * DP;
+    float v = 0.f;
+    const int row = first + r;
+    if (row < total && d < D) {
+      const int tok = row / g.heads, head = row - tok * g.heads;
+      const size_t base = (size_t)(q_row0 + tok) * g.heads + head;
+      v = d < R ? a.q_abs[base * R + d] : a.q_rot[base * g.rot_dim + (d - R)];
+    }
+    Qs[idx] = __float2bfloat16_rn(v);
+    Ks[idx] = __float2bfloat16_rn(0.f);
+  }
+  if (tid < MA_ROWS) {
+    const int row = first + tid;
+    row_pos[tid] = row < total ? q_pos0 + row / g.heads : -1;
+    row_m[tid] = -INFINITY;
+    row_l[tid] = 0.f;
+  }
+  const int32_t* bt = a.block_table + (size_t)bt_row * a.bt_stride;
+  const bool vec = (D % 8 == 0);
+  auto load_keys = [&](int k0) {
+    __syncthreads();  // the previous tile's reads of Ks / Ss / Ps are done
+    if (vec) {
+      const int cpr = D / 8;  // 16-byte chunks per key row
+      for (int idx = tid; idx < MA_KEYS * cpr; idx += MA_THREADS) {
+        const int j = idx / cpr, c = idx - j * cpr, kp = k0 + j;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (kp <= max_pos) v = ld_stream(a.cache + ((size_t)bt[kp / a.block_size] * a.block_size + kp % a.block_size) * D + c * 8);
+        *reinterpret_cast<uint4*>(Ks + j * DP + c * 8) = v;
+      }
+    } else {
+      for (int idx = tid; idx < MA_KEYS * D; idx += MA_THREADS) {
+        const int j = idx / D, d = idx - j * D, kp = k0 + j;
+        Ks[j * DP + d] = kp <= max_pos ? a.cache[((size_t)bt[kp / a.block_size] * a.block_size + kp % a.block_size) * D + d] : __float2bfloat16_rn(0.f);
+      }
+    }
+    __syncthreads();
+  };
+  // S = Q . K^T for the staged tile: warp w computes rows 16 * (w / 2) .., keys 32 * (w % 2) ..
+  auto scores = [&]() {
+    wmma::fragment<wmma::accumulator, 16, 16, 16, float> acc[2];
+    wmma::fill_fragment(acc[0], 0.f);
+    wmma::fill_fragment(acc[1], 0.f);
+    const int rm = (warp >> 1) * 16, kn = (warp & 1) * 32;
+    for (int d = 0; d < D16; d += 16) {
+      wmma::fragment<wmma::matrix_a, 16, 16, 16, bf16, wmma::row_major> fq;
+      wmma::fragment<wmma::matrix_b, 16, 16, 16, bf16, wmma::col_major> fk;
+      wmma::load_matrix_sync(fq, Qs + rm * DP + d, DP);
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        wmma::load_matrix_sync(fk, Ks + (kn + 16 * j) * DP + d, DP);
+        wmma::mma_sync(acc[j], fq, fk, acc[j]);
+      }
+    }
+    wmma::store_matrix_sync(Ss + rm * 68 + kn, acc[0], 68, wmma::mem_row_major);
+    wmma::store_matrix_sync(Ss + rm * 68 + kn + 16, acc[1], 68, wmma::mem_row_major);
+    __syncthreads();
+  };
+  // ---- sweep 1: row maxima ----
+  const int r4 = tid >> 2, q4 = tid & 3;  // four threads per row, 16 keys each
+  float mymax = -INFINITY;
+  for (int t = t_lo; t < t_hi; ++t) {
+    const int k0 = t * MA_KEYS;
+    load_keys(k0);
+    scores();
+    const int lim = row_pos[r4] - k0;  // keys j <= lim are visible
+    for (int j = q4 * 16; j < q4 * 16 + 16; ++j)
+      if (j <= lim) mymax = fmaxf(mymax, Ss[r4 * 68 + j] * g.scale);
+  }
+  mymax = fmaxf(mymax, __shfl_xor_sync(0xffffffffu, mymax, 1));
+  mymax = fmaxf(mymax, __shfl_xor_sync(0xffffffffu, mymax, 2));
+  if (q4 == 0) row_m[r4] = mymax;
+  // ---- sweep 2: P = exp(s - max), O += P . C ----
+  wmma::fragment<wmma::accumulator, 16, 16, 16, float> oacc[4][NF];   // warp w: every row, columns [w * NF * 16, (w + 1) * NF * 16)
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < NF; ++j) wmma::fill_fragment(oacc[i][j], 0.f);
+  float mysum = 0.f;
+  const int col0 = warp * NF * 16;
+  for (int t = t_lo; t < t_hi; ++t) {
+    const int k0 = t * MA_KEYS;
+    load_keys(k0);   // its first barrier also publishes row_m
+    scores();
+    const int lim = row_pos[r4] - k0;
+    const float m = row_m[r4];
+    for (int j = q4 * 16; j < q4 * 16 + 16; ++j) {
+      float p = 0.f;
+      if (j <= lim) p = expf(Ss[r4 * 68 + j] * g.scale - m);
+      const bf16 pb = __float2bfloat16_rn(p);
+      Ps[r4 * 72 + j] = pb;
+      mysum += __bfloat162float(pb);   // the weights that are summed are the weights that multiply the latents
+    }
+    __syncthreads();
+    for (int kk = 0; kk < MA_KEYS; kk += 16) {
+      wmma::fragment<wmma::matrix_a, 16, 16, 16, bf16, wmma::row_major> fp[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) wmma::load_matrix_sync(fp[i], Ps + (16 * i) * 72 + kk, 72);
+#pragma unroll
+      for (int j = 0; j < NF; ++j) {
+        if (col0 + 16 * j >= R16) continue;  // warp-uniform
+        wmma::fragment<wmma::matrix_b, 16, 16, 16, bf16, wmma::row_major> fv;
+        wmma::load_matrix_sync(fv, Ks + kk * DP + col0 + 16 * j, DP);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) wmma::mma_sync(oacc[i][j], fp[i], fv, oacc[i][j]);
+      }
+    }
+  }
+  mysum += __shfl_xor_sync(0xffffffffu, mysum, 1);
+  mysum += __shfl_xor_sync(0xffffffffu, mysum, 2);
+  __syncthreads();  // every warp is done with Qs / Ks: they become the output tile
+  if (q4 == 0) row_l[r4] = mysum;
+  const int OLD = R16 + 4;
+#pragma unroll
+  for (int j = 0; j < NF; ++j) {
+    if (col0 + 16 * j >= R16) continue;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) wmma::store_matrix_sync(Os + (16 * i) * OLD + col0 + 16 * j, oacc[i][j], OLD, wmma::mem_row_major);
+  }
+  __syncthreads();
+  for (int r = warp; r < MA_ROWS; r += MA_THREADS / 32) {
+    const int row = first + r;
+    if (row >= total) continue;
+    const int tok = row / g.heads, head = row - tok * g.heads, lane = tid & 31;
+    const size_t base = (size_t)(q_row0 + tok) * g.heads + head;
+    const float m = row_m[r], l = row_l[r];
+    if (a.nsplit == 1) {
+      const float sk = a.sink[head];
+      const float mf = fmaxf(m, sk);
+      const float corr = m == -INFINITY ? 0.f : expf(m - mf);
+      const float inv = corr / (l * corr + expf(sk - mf));
+      for (int d = lane; d < R; d += 32) a.out_lat[base * R + d] = __float2bfloat16_rn(Os[r * OLD + d] * inv);
+    } else {
+      float* dst = a.partial + (base * a.nsplit + split) * (R + 2);
+      if (lane == 0) {
+        dst[0] = m;
+        dst[1] = l;
+      }
+      for (int d = lane; d < R; d += 32) dst[2 + d] = Os[r * OLD + d];
+    }
+  }
+}
+
+// folds the splits of every (token, head) row and the sink into the output; one warp per row
+__global__ void __launch_bounds__(128) latent_merge_kernel(const float* __restrict__ partial, int nsplit, int R, int heads,
+                                                           const int32_t* __restrict__ seq_lens, const float* __restrict__ sink,
+                                                           bf16* __restrict__ out_lat, int nrows) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int row = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (row >= nrows) return;
+  const int tok = row / heads, head = row - tok * heads;
+  if (seq_lens != nullptr && seq_lens[tok] <= 0) return;
+  const float* p = partial + (size_t)row * nsplit * (R + 2);
+  const float sk = sink[head];
+  float mf = sk;
+  for (int s = 0; s < nsplit; ++s) mf = fmaxf(mf, p[(size_t)s * (R + 2)]);
+  float den = expf(sk - mf);
+  for (int s = 0; s < nsplit; ++s) {
+    const float m = p[(size_t)s * (R + 2)];
+    if (m != -INFINITY) den += p[(size_t)s * (R + 2) + 1] * expf(m - mf);
+  }
+  for (int d = lane; d < R; d += 32) {
+    float acc = 0.f;
+    for (int s = 0; s < nsplit; ++s) {
+      const float m = p[(size_t)s * (R + 2)];
+      if (m != -INFINITY) acc = fmaf(p[(size_t)s * (R + 2) + 2 + d], expf(m - mf), acc);
+    }
+    out_lat[(size_t)row * R + d] = __float2bfloat16_rn(acc / den);
+  }
+}
+
+size_t mma_attn_smem(const LatentGeom& g) {
+  const int D = g.kv_rank + g.rot_dim, DP = ((D + 15) & ~15) + 8;
+  return (size_t)2 * MA_ROWS * DP * 2 + (size_t)MA_ROWS * 68 * 4 + (size_t)MA_ROWS * 72 * 2 + 3 * MA_ROWS * 4;
+}
+
+template <int NF>
+int launch_mma(const MmaAttnArgs& a, dim3 grid, size_t smem, cudaStream_t s) {
+  static B2PerDeviceOnce once;
+  static size_t set_to = 0;
+  if (once.need() || smem > set_to) {
+    B2_CUDA_OK(cudaFuncSetAttribute(latent_attention_mma_kernel<NF>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)std::max(smem, set_to)));
+    set_to = std::max(smem, set_to);
+  }
+  B2_CUDA_OK(b2_launch(latent_attention_mma_kernel<NF>, grid, dim3(MA_THREADS), smem, s, a));
+  return 0;
+}
+
 template <typename TC, typename TX, int NR>
 int launch_la(const float* q_abs, const float* q_rot, const void* cache, const LatentGeom& g, const int32_t* block_table, int bt_stride,
               int block_size, const PrefillTile* tiles, int ntiles, const int32_t* positions, const int32_t* seq_lens, const float* sink,
@@ -258,11 +518,39 @@ int launch_latent_finish(const float* qd, int ld, const LatentGeom& g, int has_k
   return 0;
 }
 
+size_t latent_attention_scratch_floats(int max_rows, int max_heads, int max_rank) {
+  // decode steps cut the keys into splits until about two CTAs per SM exist; every (row block, split) leaves 64 rows
+  return ((size_t)2 * 148 + (size_t)max_rows * ((max_heads + MA_ROWS - 1) / MA_ROWS)) * MA_ROWS * ((size_t)max_rank + 2);
+}
+
 int launch_latent_attention(const float* q_abs, const float* q_rot, const void* cache, int cache_f32, const LatentGeom& g,
                             const int32_t* block_table, int bt_stride, int block_size, const PrefillTile* tiles, int ntiles,
                             const int32_t* positions, const int32_t* seq_lens, const float* sink, void* out_lat, int x_f32, int T,
-                            cudaStream_t s) {
+                            cudaStream_t s, float* scratch, size_t scratch_floats, int max_context) {
   if (T <= 0 || (tiles != nullptr && ntiles <= 0)) return 0;
+  static const bool use_mma = [] { const char* e = getenv("B2_LATENT_MMA"); return !(e && *e == '0'); }();
+  const size_t mma_smem = mma_attn_smem(g);
+  if (!cache_f32 && use_mma && g.kv_rank <= 512 && mma_smem <= 200 * 1024) {
+    B2_REQUIRE(x_f32 == 0, "latent_attention: operands and cache have one element type");
+    MmaAttnArgs a{q_abs, q_rot, (const bf16*)cache, g, block_table, bt_stride, block_size, tiles, positions, seq_lens, sink, (bf16*)out_lat, scratch, 1};
+    const int blocks_y = ((tiles != nullptr ? 64 : 1) * g.heads + MA_ROWS - 1) / MA_ROWS;
+    const int blocks = (tiles != nullptr ? ntiles : T) * blocks_y;
+    if (tiles == nullptr && scratch != nullptr) {   // decode: few rows, long caches -> cut the keys
+      int ns = (2 * 148) / std::max(blocks, 1);
+      ns = std::min(ns, std::max(1, (max_context + MA_KEYS - 1) / MA_KEYS));
+      while (ns > 1 && (size_t)T * g.heads * ns * (g.kv_rank + 2) > scratch_floats) --ns;
+      a.nsplit = std::max(ns, 1);
+    }
+    const dim3 grid(tiles != nullptr ? ntiles : T, blocks_y, a.nsplit);
+    const int nf = (g.kv_rank + 127) / 128;
+    if (nf <= 1) B2_TRY_RC(launch_mma<1>(a, grid, mma_smem, s));
+    else if (nf == 2) B2_TRY_RC(launch_mma<2>(a, grid, mma_smem, s));
+    else B2_TRY_RC(launch_mma<4>(a, grid, mma_smem, s));
+    if (a.nsplit > 1)
+      B2_CUDA_OK(b2_launch(latent_merge_kernel, dim3((T * g.heads + 3) / 4), dim3(128), 0, s, (const float*)scratch, a.nsplit, g.kv_rank, g.heads,
+                           seq_lens, sink, (bf16*)out_lat, T * g.heads));
+    return 0;
+  }
   B2_REQUIRE(g.kv_rank >= 1 && g.kv_rank <= 1024, "latent_attention: kv_rank %d outside [1, 1024]", g.kv_rank);
   B2_REQUIRE(x_f32 == cache_f32, "latent_attention: operands and cache have one element type");
   const size_t smem = ((size_t)LA_WARPS * (g.kv_rank + g.rot_dim) + (size_t)LA_KEYS * ((g.kv_rank + g.rot_dim) | 1)) * sizeof(float);

@@ -287,6 +287,8 @@ struct b2_engine {
   int32_t *l_idx = nullptr, *l_offsets = nullptr, *l_slot_token = nullptr, *l_pair_slot = nullptr, *l_tile_group = nullptr,
           *l_tile_row0 = nullptr, *l_ntiles = nullptr;
   int l_max_top = 0, l_tiles_cap = 0, l_rows_cap = 0;
+  float* l_attn_scratch = nullptr;   // key splits of a decode step's latent attention
+  size_t l_attn_scratch_floats = 0;
   float* dbg_hidden_f32 = nullptr;
 };
 
@@ -884,7 +886,8 @@ int forward_list(b2_engine* e, int T, int ntiles, int nlast) {
     {
       KL k(e, ntiles > 0 ? B2K_MISC : B2K_ATTN_DECODE);
       if (!k.skip()) B2_TRY(launch_latent_attention(e->l_qabs, e->l_qrot, cache_r, f, g, e->d_block_table, e->bt_stride, c.block_size, tiles, ntiles,
-                                                    e->d_positions, e->d_seq_lens, L.sink, e->l_olat, f, T, st));
+                                                    e->d_positions, e->d_seq_lens, L.sink, e->l_olat, f, T, st, e->l_attn_scratch,
+                                                    e->l_attn_scratch_floats, c.max_model_len));
     }
     {
       KL k(e, B2K_GEMM_O);  // values of every head from the weighted latent
@@ -1506,6 +1509,15 @@ int list_engine_alloc(b2_engine* e) {
   B2_TRY(dalloc(&e->l_tile_group, (size_t)e->l_tiles_cap));
   B2_TRY(dalloc(&e->l_tile_row0, (size_t)e->l_tiles_cap));
   B2_TRY(dalloc(&e->l_ntiles, (size_t)1));
+  if (!e->f32) {
+    int max_heads = 1, max_rank = 1;
+    for (const ListLayer& L : e->ll) {
+      max_heads = std::max(max_heads, L.sp.heads);
+      max_rank = std::max(max_rank, L.sp.kv_rank);
+    }
+    e->l_attn_scratch_floats = latent_attention_scratch_floats(bucket_batch(c.max_seqs), max_heads, max_rank);
+    B2_TRY(dalloc(&e->l_attn_scratch, e->l_attn_scratch_floats));
+  }
   B2_CUDA_OK(cudaMemset(e->l_ntiles, 0, 4));
   B2_CUDA_OK(cudaMemset(e->l_pair_slot, 0, Tc * max_top * 4));
   return 0;
@@ -2159,7 +2171,7 @@ extern "C" void b2_engine_free(b2_engine* e) {
   F(e->partial2); F(e->attn_scratch2); F(e->ssq);
   F(e->l_embed); F(e->l_head); F(e->l_embed_gain); F(e->l_final_gain); F(e->l_pool); F(e->l_h); F(e->l_qd); F(e->l_qrot); F(e->l_qabs);
   F(e->l_mix); F(e->l_y); F(e->l_rw); F(e->l_logits); F(e->l_x1); F(e->l_x2); F(e->l_qnope); F(e->l_olat); F(e->l_av); F(e->l_act); F(e->l_xl);
-  F(e->l_idx); F(e->l_offsets); F(e->l_slot_token); F(e->l_pair_slot); F(e->l_tile_group); F(e->l_tile_row0); F(e->l_ntiles); F(e->dbg_hidden_f32);
+  F(e->l_attn_scratch); F(e->l_idx); F(e->l_offsets); F(e->l_slot_token); F(e->l_pair_slot); F(e->l_tile_group); F(e->l_tile_row0); F(e->l_ntiles); F(e->dbg_hidden_f32);
   for (auto& L : e->ll) {
     F(L.wqd); F(L.ukT); F(L.uv); F(L.wo); F(L.up); F(L.down); F(L.gain1); F(L.gain2); F(L.lat_gain); F(L.sink); F(L.router); F(L.corr);
   }

@@ -265,7 +265,10 @@ int launch_latent_finish(const float* qd, int ld, const LatentGeom& g, int has_k
 int launch_latent_attention(const float* q_abs, const float* q_rot, const void* cache, int cache_f32, const LatentGeom& g,
                             const int32_t* block_table, int bt_stride, int block_size, const PrefillTile* tiles, int ntiles,
                             const int32_t* positions, const int32_t* seq_lens, const float* sink, void* out_lat, int x_f32, int T,
-                            cudaStream_t s);
+                            cudaStream_t s, float* scratch = nullptr, size_t scratch_floats = 0, int max_context = 0);
+// scratch: device floats for the key splits of a decode step (latent_attention_scratch_floats); without it a decode step runs
+// unsplit.  max_context: longest cache the engine can hold (bounds the number of splits).
+size_t latent_attention_scratch_floats(int max_rows, int max_heads, int max_rank);
 
 // ---- moe_route.cu: sigmoid router with a choice offset and grouped selection, and the token permutation by expert ----
 struct RouteGeom {

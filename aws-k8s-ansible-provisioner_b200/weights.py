@@ -63,3 +63,48 @@ def write_safetensors(sd: dict[str, torch.Tensor], path: str) -> None:
         for t in sd.values():
             t = t.contiguous()
             f.write(t.view(torch.int16 if t.element_size() == 2 else torch.int32).numpy().tobytes())
+
+
+def lerasun_tensor_shapes(model_cfg: dict) -> dict[str, tuple[int, ...]]:
+    """Tensor names and shapes of a Lerasun checkpoint for the dict its config.json holds."""
+    W, V = model_cfg["width"], model_cfg["vocab"]
+    s: dict[str, tuple[int, ...]] = {"embed": (V, W), "embed.norm": (W,)}
+    for i, layer in enumerate(model_cfg["layers"]):
+        m, mlp, p = layer["mixer"], layer.get("mlp"), f"l{i}."
+        H, dn, dr, dv, r = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
+        s[p + "norm1"] = (W,)
+        s[p + "mix.q"] = (H * (dn + dr), W)
+        if m.get("kv_from") is None:
+            s[p + "mix.dkv"] = (r + dr, W)
+            s[p + "mix.dkv.norm"] = (r,)
+        s[p + "mix.uk"] = (H * dn, r)
+        s[p + "mix.uv"] = (H * dv, r)
+        s[p + "mix.sink"] = (H,)
+        s[p + "mix.o"] = (W, H * dv)
+        if mlp is not None:
+            s[p + "norm2"] = (W,)
+            for e in range(mlp["router"]["experts"]):
+                s[p + f"mlp.e{e}.up"] = (mlp["expert"]["ff"], W)
+                s[p + f"mlp.e{e}.down"] = (W, mlp["expert"]["ff"])
+            s[p + "mlp.router"] = (mlp["router"]["experts"], W)
+            s[p + "mlp.correction"] = (mlp["router"]["experts"],)
+    s["final.norm"] = (W,)
+    s["head"] = (V, W)
+    return s
+
+
+def lerasun_random_state_dict(model_cfg: dict, seed: int = 0) -> dict[str, torch.Tensor]:
+    """Random bf16 weights scaled by 1/sqrt(fan-in) (gains and offsets small), so activations stay O(1) at any depth."""
+    g = torch.Generator().manual_seed(seed)
+    sd = {}
+    for name, shape in lerasun_tensor_shapes(model_cfg).items():
+        if name.endswith("dkv.norm"):
+            t = 1.0 + 0.1 * torch.randn(shape, generator=g)
+        elif "norm" in name or name.endswith(("sink", "correction")):
+            t = 0.1 * torch.randn(shape, generator=g)
+        elif name == "embed":
+            t = torch.randn(shape, generator=g)
+        else:
+            t = torch.randn(shape, generator=g) * (shape[-1] ** -0.5)
+        sd[name] = t.to(torch.bfloat16)
+    return sd

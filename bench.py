@@ -434,6 +434,72 @@ def run_b200(args, rank, world, local, dist):
         print(json.dumps(line), flush=True)
 
 
+# ---- --family lerasun: the layer-list family beside the closest GQA model at equal size (informational; one GPU) ----
+FAMILY_SIZES = {   # width, heads, kv_rank, experts, top, expert ff, groups, kept groups   (dim 128 | rot 64, vdim 128, 4 layers, vocab 32000)
+    "w1024": (1024, 8, 256, 8, 2, 768, 1, 1),
+    "w2048": (2048, 16, 512, 16, 4, 704, 4, 2),
+    "w4096": (4096, 32, 512, 16, 4, 1024, 4, 2),
+}
+
+
+def lerasun_model_cfg(width, heads, rank, experts, top, ff, groups, keep, layers=4, vocab=32000):
+    mixer = {"heads": heads, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": rank, "scale": 192 ** -0.5, "rot": {"base": 10000.0, "dims": 64}}
+    mlp = {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": experts, "top": top, "groups": {"count": groups, "keep": keep}}}
+    ls = [{"type": "latent_attention", "mixer": dict(mixer, **({"kv_from": i - 1} if i % 2 else {})), "mlp": mlp} for i in range(layers)]
+    return {"architecture": "Lerasun", "vocab": vocab, "width": width, "logit_scale": 1.0, "norm": {"eps": 1e-6}, "layers": ls}
+
+
+def run_family(args, local):
+    """Prefill and decode throughput of Lerasun at layer sizes of real models (random weights), and of Qwen3 at the same
+    width, depth, head count and active feed-forward size: one JSON line per size and model, with the decode step's
+    per-kernel-class times (CUDA events around every launch of an eager step)."""
+    import torch
+
+    pkg = importlib.import_module(PKG)
+    weights = importlib.import_module(PKG + ".weights")
+    B, PL, NEW = args.family_batch, args.family_prompt, 72
+    peaks = measured_peaks()
+    for tag in args.family_sizes.split(","):
+        width, heads, rank, experts, top, ff, groups, keep = FAMILY_SIZES[tag]
+        mc = lerasun_model_cfg(width, heads, rank, experts, top, ff, groups, keep)
+        inter = ((2 * top * ff // 3) + 255) // 256 * 256      # SwiGLU with the same active feed-forward parameters
+        models = [("lerasun", pkg.EngineConfig.lerasun(mc), lambda c: weights.lerasun_random_state_dict(mc, seed=0)),
+                  ("qwen3", pkg.EngineConfig(num_layers=4, hidden=width, num_q_heads=heads, num_kv_heads=heads // 2, head_dim=128,
+                                             intermediate=inter, vocab=32000), lambda c: weights.random_state_dict(c, seed=0))]
+        for name, cfg, make_sd in models:
+            cfg.max_model_len, cfg.max_seqs, cfg.max_batch_tokens, cfg.use_cuda_graphs = PL + NEW + 16, B, B * PL, True
+            cfg.num_blocks = B * ((cfg.max_model_len + 15) // 16) + 8
+            sd = make_sd(cfg)
+            nparams = sum(v.numel() for v in sd.values())
+            eng = pkg.Engine(cfg, device=local)
+            eng.load_state_dict(sd)
+            del sd
+            g = torch.Generator().manual_seed(1)
+            prompts = torch.randint(0, cfg.vocab, (B, PL), generator=g, dtype=torch.int32).numpy()
+            times = []
+            for rep in range(3):          # the first call warms every kernel; best of the rest
+                sids = [eng.seq_create(cfg.max_model_len) for _ in range(B)]
+                torch.cuda.synchronize(local)
+                t0 = time.perf_counter()
+                eng.prefill(sids, [p.tolist() for p in prompts])
+                times.append(time.perf_counter() - t0)
+                if rep < 2:
+                    for s_ in sids:
+                        eng.seq_free(s_)
+            prefill_s = min(times[1:])
+            eng.decode_run(sids, 8, want_tokens=False)
+            _, ms = eng.decode_run(sids, NEW - 16, want_tokens=False)
+            ms_step = ms / (NEW - 16)
+            prof = eng.decode_profile(sids, 4)
+            print(json.dumps({"family_bench": tag, "model": name, "params": nparams, "batch": B, "prompt": PL,
+                              "prefill_tok_s": round(B * PL / prefill_s), "prefill_ms": round(prefill_s * 1e3, 2),
+                              "decode_tok_s": round(B / ms_step * 1e3), "decode_ms_per_step": round(ms_step, 4),
+                              "decode_class_us_per_step": {k: round(v["ms"] / 4 * 1e3, 1) for k, v in prof.items() if v["launches"]},
+                              "decode_launches_per_step": sum(v["launches"] for v in prof.values()) // 4,
+                              "peaks": peaks}), flush=True)
+            eng.close()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -442,7 +508,15 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--value-only", action="store_true", help="device-resident timing only (ablation runs)")
+    ap.add_argument("--family", default="", choices=["", "lerasun"],
+                    help="instead of the headline workload: the named family beside the closest GQA model at equal size (one GPU)")
+    ap.add_argument("--family-sizes", default="w1024,w2048,w4096")
+    ap.add_argument("--family-batch", type=int, default=16)
+    ap.add_argument("--family-prompt", type=int, default=1024)
     args = ap.parse_args()
+    if args.family:
+        run_family(args, int(os.environ.get("LOCAL_RANK", "0")))
+        return
     rank, world, local, dist = dist_setup(args.gpus)
     try:
         if args.impl == "reference":
