@@ -275,17 +275,17 @@ __global__ void __launch_bounds__(MA_THREADS, 1) latent_attention_mma_kernel(Mma
   const int t_lo = split * per, t_hi = min(ntile, t_lo + per);
 
   // ---- stage Q (bf16), zero the padding columns of both operand slabs ----
-  for (int idx = tid; idx < MA_ROWS * DP; idx += MA_THREADS) {
-    const int r = idx / DP, d = idx - r * DP;
-    float v = 0.f;
-    const int row = first + r;
-    if (row < total && d < D) {
-      const int tok = row / g.heads, head = row - tok * g.heads;
-      const size_t base = (size_t)(q_row0 + tok) * g.heads + head;
-      v = d < R ? a.q_abs[base * R + d] : a.q_rot[base * g.rot_dim + (d - R)];
+  for (int r = warp; r < MA_ROWS; r += MA_THREADS / 32) {
+    const int row = first + r, lane = tid & 31;
+    const bool live = row < total;
+    const int tok = live ? row / g.heads : 0, head = live ? row - tok * g.heads : 0;
+    const size_t base = (size_t)(q_row0 + tok) * g.heads + head;
+    for (int d = lane; d < DP; d += 32) {
+      float v = 0.f;
+      if (live && d < D) v = d < R ? a.q_abs[base * R + d] : a.q_rot[base * g.rot_dim + (d - R)];
+      Qs[r * DP + d] = __float2bfloat16_rn(v);
+      Ks[r * DP + d] = __float2bfloat16_rn(0.f);
     }
-    Qs[idx] = __float2bfloat16_rn(v);
-    Ks[idx] = __float2bfloat16_rn(0.f);
   }
   if (tid < MA_ROWS) {
     const int row = first + tid;
@@ -430,20 +430,21 @@ __global__ void __launch_bounds__(128) latent_merge_kernel(const float* __restri
   if (seq_lens != nullptr && seq_lens[tok] <= 0) return;
   const float* p = partial + (size_t)row * nsplit * (R + 2);
   const float sk = sink[head];
-  float mf = sk;
-  for (int s = 0; s < nsplit; ++s) mf = fmaxf(mf, p[(size_t)s * (R + 2)]);
-  float den = expf(sk - mf);
-  for (int s = 0; s < nsplit; ++s) {
-    const float m = p[(size_t)s * (R + 2)];
-    if (m != -INFINITY) den += p[(size_t)s * (R + 2) + 1] * expf(m - mf);
-  }
-  for (int d = lane; d < R; d += 32) {
+  // lane s holds split s (nsplit <= 32): its maximum, then its weight exp(m_s - m)
+  const float m_s = lane < nsplit ? p[(size_t)lane * (R + 2)] : -INFINITY;
+  const float l_s = lane < nsplit ? p[(size_t)lane * (R + 2) + 1] : 0.f;
+  const float mf = fmaxf(warp_max(m_s), sk);
+  const float w_s = m_s == -INFINITY ? 0.f : expf(m_s - mf);
+  const float inv = 1.0f / (warp_sum(l_s * w_s) + expf(sk - mf));
+  for (int d0 = 0; d0 < R; d0 += 32) {
+    const int d = d0 + lane;
     float acc = 0.f;
+#pragma unroll 4
     for (int s = 0; s < nsplit; ++s) {
-      const float m = p[(size_t)s * (R + 2)];
-      if (m != -INFINITY) acc = fmaf(p[(size_t)s * (R + 2) + 2 + d], expf(m - mf), acc);
+      const float w = __shfl_sync(0xffffffffu, w_s, s);
+      if (d < R && w != 0.f) acc = fmaf(p[(size_t)s * (R + 2) + 2 + d], w, acc);
     }
-    out_lat[(size_t)row * R + d] = __float2bfloat16_rn(acc / den);
+    if (d < R) out_lat[(size_t)row * R + d] = __float2bfloat16_rn(acc * inv);
   }
 }
 
@@ -537,7 +538,7 @@ int launch_latent_attention(const float* q_abs, const float* q_rot, const void* 
     const int blocks = (tiles != nullptr ? ntiles : T) * blocks_y;
     if (tiles == nullptr && scratch != nullptr) {   // decode: few rows, long caches -> cut the keys
       int ns = (2 * 148) / std::max(blocks, 1);
-      ns = std::min(ns, std::max(1, (max_context + MA_KEYS - 1) / MA_KEYS));
+      ns = std::min(std::min(ns, 32), std::max(1, (max_context + MA_KEYS - 1) / MA_KEYS));
       while (ns > 1 && (size_t)T * g.heads * ns * (g.kv_rank + 2) > scratch_floats) --ns;
       a.nsplit = std::max(ns, 1);
     }

@@ -286,7 +286,7 @@ struct b2_engine {
   void *l_x1 = nullptr, *l_x2 = nullptr, *l_qnope = nullptr, *l_olat = nullptr, *l_av = nullptr, *l_act = nullptr, *l_xl = nullptr;
   int32_t *l_idx = nullptr, *l_offsets = nullptr, *l_slot_token = nullptr, *l_pair_slot = nullptr, *l_tile_group = nullptr,
           *l_tile_row0 = nullptr, *l_ntiles = nullptr;
-  int l_max_top = 0, l_tiles_cap = 0, l_rows_cap = 0;
+  int l_max_top = 0, l_tiles_cap = 0, l_rows_cap = 0, l_offsets_stride = 0;
   float* l_attn_scratch = nullptr;   // key splits of a decode step's latent attention
   size_t l_attn_scratch_floats = 0;
   float* dbg_hidden_f32 = nullptr;
@@ -911,7 +911,7 @@ int forward_list(b2_engine* e, int T, int ntiles, int nlast) {
       }
       {
         KL k(e, B2K_MISC);
-        if (!k.skip()) B2_TRY(launch_route_permute(e->l_idx, T, sp.top, sp.experts, e->l_offsets, e->l_slot_token, e->l_pair_slot, st));
+        if (!k.skip()) B2_TRY(launch_route_permute(e->l_idx, T, sp.top, sp.experts, e->l_offsets, e->l_offsets_stride, e->l_slot_token, e->l_pair_slot, st));
       }
       const int max_tiles = std::min(e->l_tiles_cap, (T * sp.top + any_gemm_tile_rows() - 1) / any_gemm_tile_rows() + sp.experts);
       {
@@ -924,13 +924,13 @@ int forward_list(b2_engine* e, int T, int ntiles, int nlast) {
         KL k(e, B2K_GEMM_GATEUP);  // act[slot] = relu(U_e x[token(slot)])^2
         a.A = e->l_x2; a.a_rows = e->l_slot_token; a.W = L.up; a.C = e->l_act; a.N = sp.ff_dim; a.K = W; a.lda = W; a.ldw = W; a.ldc = sp.ff_dim;
         a.w_bs = (long)sp.ff_dim * W; a.epilogue = ANY_EPI_RELU2;
-        if (!k.skip()) B2_TRY(launch_gemm_any(a, f, f, f, 1, max_tiles, st));
+        if (!k.skip()) B2_TRY(launch_gemm_any(a, f, f, f, 1, max_tiles, st, T * sp.top, sp.experts));
       }
       {
         KL k(e, B2K_GEMM_DOWN);  // y[slot] = D_e act[slot]
         a.A = e->l_act; a.a_rows = nullptr; a.W = L.down; a.C = e->l_y; a.N = W; a.K = sp.ff_dim; a.lda = sp.ff_dim; a.ldw = sp.ff_dim; a.ldc = W;
         a.w_bs = (long)W * sp.ff_dim; a.epilogue = ANY_EPI_STORE;
-        if (!k.skip()) B2_TRY(launch_gemm_any(a, f, f, 1, 1, max_tiles, st));
+        if (!k.skip()) B2_TRY(launch_gemm_any(a, f, f, 1, 1, max_tiles, st, T * sp.top, sp.experts));
       }
     }
     {
@@ -1502,7 +1502,9 @@ int list_engine_alloc(b2_engine* e) {
   B2_TRY(aalloc(&e->l_act, Tc * max_top * max_ff));
   B2_TRY(aalloc(&e->l_xl, (size_t)e->l_rows_cap * W));
   B2_TRY(dalloc(&e->l_idx, Tc * max_top));
-  B2_TRY(dalloc(&e->l_offsets, (size_t)max_exp + 1));
+  e->l_offsets_stride = max_exp + 1;
+  B2_TRY(dalloc(&e->l_offsets, (size_t)3 * (max_exp + 1)));
+  B2_CUDA_OK(cudaMemset(e->l_offsets, 0, (size_t)3 * (max_exp + 1) * 4));
   B2_TRY(dalloc(&e->l_slot_token, Tc * max_top));
   B2_TRY(dalloc(&e->l_pair_slot, Tc * max_top));
   e->l_tiles_cap = (int)(Tc * max_top / any_gemm_tile_rows() + max_exp + 1);

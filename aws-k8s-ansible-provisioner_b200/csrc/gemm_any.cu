@@ -19,6 +19,11 @@
 // fp32 accumulators, four warps of 32 x 32 outputs, 64 x 32 operand slabs staged with 16-byte loads when rows are
 // 16-byte aligned and element by element when they are not); the fp32 form stays on plain FMAs because a true-fp32
 // product has no tensor-core mode.  Same grid, same epilogues, same independence of a row from its tile mates.
+//
+// Few rows (a decode step: M <= 64 per batch, or experts that see a handful of tokens each) take gemm_any_rows_kernel
+// instead: the product is then a stream of weights, not arithmetic.  The rows are staged in shared memory once per CTA,
+// every warp walks two weight rows at a time with 16-byte loads (eight in flight per lane) and keeps one accumulator per
+// staged row; a CTA covers 8 weight rows, so N / 8 CTAs (times batches or experts) pull on HBM at once.
 #include <mma.h>
 
 #include "kernels.h"
@@ -226,6 +231,152 @@ __global__ void __launch_bounds__(128) gemm_any_mma_kernel(AnyGemm g) {
   }
 }
 
+// ---- few rows: weight-streaming form ----
+constexpr int RB = 16, ROWS_NPB = 8;   // staged rows per pass; weight rows per CTA (4 warps x one pair)
+
+template <typename T>
+__device__ __forceinline__ void load8(const T* p, int k, int K, bool vec, float* f);
+template <>
+__device__ __forceinline__ void load8<bf16>(const bf16* p, int k, int K, bool vec, float* f) {
+  if (vec && k + 8 <= K) {
+    unpack8(*reinterpret_cast<const uint4*>(p + k), f);
+  } else {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) f[j] = k + j < K ? __bfloat162float(p[k + j]) : 0.f;
+  }
+}
+template <>
+__device__ __forceinline__ void load8<float>(const float* p, int k, int K, bool vec, float* f) {
+  if (vec && k + 8 <= K) {
+    const float4 a = *reinterpret_cast<const float4*>(p + k), b = *reinterpret_cast<const float4*>(p + k + 4);
+    f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+  } else {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) f[j] = k + j < K ? p[k + j] : 0.f;
+  }
+}
+
+template <typename TA, typename TW, typename TC>
+__global__ void __launch_bounds__(128) gemm_any_rows_kernel(AnyGemm g, int rows_per_pass) {
+  extern __shared__ __align__(16) unsigned char rows_smem[];   // [rows_per_pass][Kp] of TA, Kp = K rounded up to 8
+  TA* As = reinterpret_cast<TA*>(rows_smem);
+  pdl_wait();
+  pdl_launch_dependents();
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const TA* A = reinterpret_cast<const TA*>(g.A);
+  const TW* W = reinterpret_cast<const TW*>(g.W);
+  TC* C = reinterpret_cast<TC*>(g.C);
+  int row_lo, row_hi;
+  if (g.group_offsets != nullptr) {   // ragged: blockIdx.y = group
+    row_lo = g.group_offsets[blockIdx.y];
+    row_hi = g.group_offsets[blockIdx.y + 1];
+    if (row_lo >= row_hi) return;
+    W += (size_t)blockIdx.y * g.w_bs;
+  } else {
+    row_lo = 0;
+    row_hi = g.M;
+    A += (size_t)blockIdx.z * g.a_bs;
+    W += (size_t)blockIdx.z * g.w_bs;
+    C += (size_t)blockIdx.z * g.c_bs;
+  }
+  const int K = g.K, Kp = (K + 7) & ~7;
+  const bool a_vec = (g.lda % 8 == 0) && ((reinterpret_cast<uintptr_t>(A) & 31) == 0);
+  const bool w_vec = (g.ldw % 8 == 0) && ((reinterpret_cast<uintptr_t>(W) & 31) == 0);
+  const int n_base = blockIdx.x * ROWS_NPB;
+  for (int r0 = row_lo; r0 < row_hi; r0 += rows_per_pass) {
+    const int rb = min(rows_per_pass, row_hi - r0);
+    __syncthreads();
+    for (int idx = tid; idx < rb * (Kp / 8); idx += 128) {
+      const int m = idx / (Kp / 8), k = (idx - m * (Kp / 8)) * 8;
+      const long ar = g.a_rows ? (long)g.a_rows[r0 + m] : (long)(r0 + m);
+      const TA* src = A + ar * g.lda;
+      TA* dst = As + (size_t)m * Kp + k;
+      if (a_vec && k + 8 <= K) {
+        if constexpr (sizeof(TA) == 2) *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(src + k);
+        else { *reinterpret_cast<float4*>(dst) = *reinterpret_cast<const float4*>(src + k); *reinterpret_cast<float4*>(dst + 4) = *reinterpret_cast<const float4*>(src + k + 4); }
+      } else {
+        for (int j = 0; j < 8; ++j) dst[j] = k + j < K ? src[k + j] : (TA)0.f;
+      }
+    }
+    __syncthreads();
+    {   // this warp's pair of weight rows
+      const int n = n_base + warp * 2;
+      if (n < g.N) {
+        const bool two = n + 1 < g.N;
+        const TW* w0 = W + (long)n * g.ldw;
+        const TW* w1 = W + (long)(two ? n + 1 : n) * g.ldw;
+        float acc[2 * RB];   // [m] row n, [RB + m] row n + 1
+#pragma unroll
+        for (int m = 0; m < 2 * RB; ++m) acc[m] = 0.f;
+        float f0[8], f1[8], g0[8], g1[8];
+        int k = lane * 8;
+        if (k < Kp) { load8<TW>(w0, k, K, w_vec, f0); load8<TW>(w1, k, K, w_vec, f1); }
+        for (; k < Kp; k += 256) {
+          const int kn = k + 256;
+          if (kn < Kp) { load8<TW>(w0, kn, K, w_vec, g0); load8<TW>(w1, kn, K, w_vec, g1); }   // next step's weights are in flight
+#pragma unroll
+          for (int m = 0; m < RB; ++m) {
+            if (m < rb) {
+              float fa[8];
+              load8<TA>(As + (size_t)m * Kp, k, Kp, true, fa);
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                acc[m] = fmaf(fa[j], f0[j], acc[m]);
+                acc[RB + m] = fmaf(fa[j], f1[j], acc[RB + m]);
+              }
+            }
+          }
+#pragma unroll
+          for (int j = 0; j < 8; ++j) { f0[j] = g0[j]; f1[j] = g1[j]; }
+        }
+        // 32 sums over 32 lanes in 31 shuffles: each round halves the values a lane holds; lane L ends with value L
+#pragma unroll
+        for (int o = 16; o >= 1; o >>= 1) {
+          const bool upper = (lane & o) != 0;
+#pragma unroll
+          for (int i = 0; i < o; ++i) {
+            const float send = upper ? acc[i] : acc[i + o];
+            const float keep = upper ? acc[i + o] : acc[i];
+            acc[i] = keep + __shfl_xor_sync(0xffffffffu, send, o);
+          }
+        }
+        // (round o keeps, in a lane whose bit o is set, the upper half of the values it still holds: lane L ends with value L)
+        const int m = lane & (RB - 1), which = lane >> 4;   // value L = which * RB + m
+        if (m < rb && (which == 0 || two)) {
+          float v = acc[0] * g.alpha;
+          TC* dst = C + (size_t)(r0 + m) * g.ldc + n + which;
+          if (g.epilogue == ANY_EPI_RELU2) {
+            v = fmaxf(v, 0.f);
+            v = v * v;
+          }
+          if (g.epilogue == ANY_EPI_ADD) {
+            if constexpr (sizeof(TC) == 4) *dst = (TC)((float)*dst + v);
+          } else {
+            if constexpr (sizeof(TC) == 4) *dst = v;
+            else *dst = __float2bfloat16_rn(v);
+          }
+        }
+      }
+    }
+  }
+}
+
+template <typename TA, typename TW, typename TC>
+int launch_rows(const AnyGemm& g, int groups, int batch, cudaStream_t s) {
+  const int Kp = (g.K + 7) & ~7;
+  int rpp = std::min<long>(RB, (long)(96 * 1024) / ((long)Kp * (long)sizeof(TA)));
+  if (rpp < 1) return 1;   // a single row does not fit: the caller uses the tile form
+  const size_t smem = (size_t)rpp * Kp * sizeof(TA);
+  auto kern = gemm_any_rows_kernel<TA, TW, TC>;
+  if (smem > 48 * 1024) {
+    static B2PerDeviceOnce once;
+    if (once.need()) B2_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
+  }
+  const dim3 grid((g.N + ROWS_NPB - 1) / ROWS_NPB, groups > 0 ? groups : 1, groups > 0 ? 1 : (batch > 0 ? batch : 1));
+  B2_CUDA_OK(b2_launch(kern, grid, dim3(128), smem, s, g, rpp));
+  return 0;
+}
+
 // One CTA: tiles of the ragged groups.  group_offsets [G + 1] -> (tile_group, tile_row0, n_tiles).
 __global__ void ragged_tiles_kernel(const int* __restrict__ group_offsets, int G, int* __restrict__ tile_group, int* __restrict__ tile_row0,
                                     int* __restrict__ n_tiles, int cap) {
@@ -251,9 +402,21 @@ int launch_ragged_tiles(const int* group_offsets, int G, int* tile_group, int* t
   return 0;
 }
 
-int launch_gemm_any(const AnyGemm& g, int a_f32, int w_f32, int c_f32, int batch, int max_tiles, cudaStream_t s) {
+int launch_gemm_any(const AnyGemm& g, int a_f32, int w_f32, int c_f32, int batch, int max_tiles, cudaStream_t s, int ragged_rows, int groups) {
   if (g.N <= 0 || g.K <= 0) return 0;
   B2_REQUIRE(g.epilogue != ANY_EPI_ADD || c_f32, "gemm_any: the add epilogue needs an fp32 C");
+  {  // few rows: stream the weights (rows of every group counted together for the ragged form: they bound the work per group)
+    static const bool use_rows = [] { const char* e = getenv("B2_ANY_ROWS"); return !(e && *e == '0'); }();
+    const bool ragged = g.tile_group != nullptr;
+    const bool few = ragged ? (ragged_rows > 0 && ragged_rows <= 8 * RB && groups > 0) : (g.M > 0 && g.M <= 4 * RB);
+    if (use_rows && few && a_f32 == w_f32) {
+      int rc = 1;
+      if (a_f32 && c_f32) rc = launch_rows<float, float, float>(g, ragged ? groups : 0, batch, s);
+      else if (!a_f32 && c_f32) rc = launch_rows<bf16, bf16, float>(g, ragged ? groups : 0, batch, s);
+      else if (!a_f32 && !c_f32) rc = launch_rows<bf16, bf16, bf16>(g, ragged ? groups : 0, batch, s);
+      if (rc <= 0) return rc;
+    }
+  }
   dim3 grid;
   if (g.tile_group != nullptr) {
     if (max_tiles <= 0) return 0;

@@ -233,8 +233,11 @@ struct AnyGemm {
 };
 int any_gemm_tile_rows();
 int launch_ragged_tiles(const int* group_offsets, int G, int* tile_group, int* tile_row0, int* n_tiles, int cap, cudaStream_t s);
-// *_f32: element type of A / W / C (1 = fp32, 0 = bf16); batch: strided batches (dense); max_tiles: capacity of the tile list (ragged)
-int launch_gemm_any(const AnyGemm& g, int a_f32, int w_f32, int c_f32, int batch, int max_tiles, cudaStream_t s);
+// *_f32: element type of A / W / C (1 = fp32, 0 = bf16); batch: strided batches (dense); max_tiles: capacity of the tile list (ragged);
+// ragged_rows / groups: total rows over all groups and the number of groups (ragged), which let a launch with few rows take the
+// weight-streaming form (0 = always tiles)
+int launch_gemm_any(const AnyGemm& g, int a_f32, int w_f32, int c_f32, int batch, int max_tiles, cudaStream_t s, int ragged_rows = 0,
+                    int groups = 0);
 
 // ---- resid_f32.cu: an fp32 residual stream and the unit-offset RMS norm x / rms(x) * (1 + g) around it ----
 // gains are fp32 and hold 1 + g already.  Outputs are fp32 or bf16 (x_f32).
@@ -277,10 +280,11 @@ struct RouteGeom {
 // x [T][W] (operand type), router [experts][W] fp32, correction [experts] fp32 -> idx [T][top], weight [T][top]
 int launch_route(const void* x, int x_f32, const float* router, const float* correction, const RouteGeom& g, int32_t* idx, float* weight,
                  int T, int W, cudaStream_t s);
-// counting sort of the T*top (token, choice) pairs by expert: offsets [experts + 1], slot_token [T*top] (slot -> token),
-// pair_slot [T*top] (pair -> slot).  Deterministic: pairs of an expert keep their (token, choice) order.
-int launch_route_permute(const int32_t* idx, int T, int top, int experts, int32_t* offsets, int32_t* slot_token, int32_t* pair_slot,
-                         cudaStream_t s);
+// counting sort of the T*top (token, choice) pairs by expert: offsets [experts + 1] (the buffer holds 3 * stride ints,
+// stride >= experts + 1: the kernels keep a histogram and a cursor behind the offsets, at offsets + stride and
+// offsets + 2 * stride; zero it once when it is allocated), slot_token [T*top] (slot -> token), pair_slot [T*top] (pair -> slot).
+int launch_route_permute(const int32_t* idx, int T, int top, int experts, int32_t* offsets, int stride, int32_t* slot_token,
+                         int32_t* pair_slot, cudaStream_t s);
 // h[t] += sum_k weight[t][k] * y[pair_slot[t*top + k]]   (+ mix[t] when given); fp32
 int launch_route_combine(float* h, const float* mix, const float* y, const float* weight, const int32_t* pair_slot, int T, int W, int top,
                          cudaStream_t s);

@@ -7,10 +7,11 @@
 // are out, not zero).  Of the allowed experts the `top` with the best choice scores are taken; their s, divided by their
 // sum (+ 1e-20), are the weights.  Ties go to the lower index.
 //
-// route_permute is a stable counting sort of the (token, choice) pairs by expert: slots of expert e are
-// [offsets[e], offsets[e+1]), in (token, choice) order, so the order of the rows inside an expert's GEMM -- and with it
-// every sum -- does not depend on the other requests of the batch.  route_combine adds the weighted expert outputs (and the
-// mixer branch) onto the fp32 residual stream in choice order.
+// route_permute is a counting sort of the (token, choice) pairs by expert: slots of expert e are [offsets[e], offsets[e+1]).
+// Which slot of its expert a pair gets depends on the order of atomic arrivals, and that is harmless: gemm_any.cu sums every
+// output row on its own, so a row's result does not depend on its slot or on its tile mates -- nor, therefore, on the other
+// requests of the batch.  route_combine adds the weighted expert outputs (and the mixer branch) onto the fp32 residual
+// stream in choice order.
 #include "kernels.h"
 
 namespace b2 {
@@ -19,24 +20,37 @@ namespace {
 
 constexpr int RT_WARPS = 4;
 
+// one CTA per token: the row is staged once as fp32, warp w takes experts w, w + 4, ...; thread 0 then selects
 template <typename TX>
 __global__ void __launch_bounds__(RT_WARPS * 32) route_kernel(const TX* __restrict__ x, const float* __restrict__ router,
                                                               const float* __restrict__ correction, RouteGeom g, int32_t* __restrict__ idx,
                                                               float* __restrict__ weight, int T, int W) {
-  extern __shared__ float sm[];  // per warp: s [E], choice [E]
+  extern __shared__ float sm[];  // s [E], choice [E], x row [W]
   pdl_wait();
   pdl_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int t = blockIdx.x * RT_WARPS + warp;
-  if (t >= T) return;
+  const int t = blockIdx.x;
   const int E = g.experts;
-  float* s = sm + (size_t)warp * 2 * E;
+  float* s = sm;
   float* ch = s + E;
+  float* xs = ch + E;
   const TX* xr = x + (size_t)t * W;
-  for (int e = 0; e < E; ++e) {
+  for (int i = threadIdx.x; i < W; i += RT_WARPS * 32) xs[i] = (float)xr[i];
+  __syncthreads();
+  const bool vec = (W % 4 == 0);
+  for (int e = warp; e < E; e += RT_WARPS) {
     const float* rr = router + (size_t)e * W;
     float acc = 0.f;
-    for (int i = lane; i < W; i += 32) acc = fmaf((float)xr[i], rr[i], acc);
+    if (vec) {
+#pragma unroll 4
+      for (int i = lane * 4; i < W; i += 128) {
+        const float4 r4 = *reinterpret_cast<const float4*>(rr + i);
+        const float4 x4 = *reinterpret_cast<const float4*>(xs + i);
+        acc = fmaf(x4.x, r4.x, acc); acc = fmaf(x4.y, r4.y, acc); acc = fmaf(x4.z, r4.z, acc); acc = fmaf(x4.w, r4.w, acc);
+      }
+    } else {
+      for (int i = lane; i < W; i += 32) acc = fmaf(xs[i], rr[i], acc);
+    }
     acc = warp_sum(acc);
     if (lane == 0) {
       const float sg = 1.0f / (1.0f + expf(-acc));
@@ -44,8 +58,8 @@ __global__ void __launch_bounds__(RT_WARPS * 32) route_kernel(const TX* __restri
       ch[e] = sg + correction[e];
     }
   }
-  __syncwarp();
-  if (lane != 0) return;
+  __syncthreads();
+  if (threadIdx.x != 0) return;
   // groups: score = sum of the two best choice scores; all but the `keep` best are out (choice = -inf).  Ranks are formed
   // from the untouched scores first (a 64-bit mask remembers who is out), then applied.
   const int per = E / g.groups;
@@ -89,50 +103,41 @@ __global__ void __launch_bounds__(RT_WARPS * 32) route_kernel(const TX* __restri
   for (int k = 0; k < g.top; ++k) weight[(size_t)t * g.top + k] *= inv;
 }
 
-// one CTA; warp w owns experts w, w + nwarps, ...
-__global__ void __launch_bounds__(1024) route_permute_kernel(const int32_t* __restrict__ idx, int npairs, int top, int E,
-                                                             int32_t* __restrict__ offsets, int32_t* __restrict__ slot_token,
-                                                             int32_t* __restrict__ pair_slot) {
-  extern __shared__ int cnt[];  // [E + 1]
+// the permutation in three steps: histogram (any number of CTAs), scan (one thread; experts are few), placement
+__global__ void __launch_bounds__(256) route_count_kernel(const int32_t* __restrict__ idx, int npairs, int E, int* __restrict__ counts) {
+  extern __shared__ int hist[];
   pdl_wait();
   pdl_launch_dependents();
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
-  for (int e = warp; e < E; e += nw) {
-    int c = 0;
-    for (int p0 = 0; p0 < npairs; p0 += 32) {
-      const int p = p0 + lane;
-      const bool hit = p < npairs && idx[p] == e;
-      c += __popc(__ballot_sync(0xffffffffu, hit));
-    }
-    if (lane == 0) cnt[e] = c;
-  }
+  for (int e = threadIdx.x; e < E; e += 256) hist[e] = 0;
   __syncthreads();
-  if (threadIdx.x == 0) {
-    int run = 0;
-    for (int e = 0; e < E; ++e) {
-      const int c = cnt[e];
-      cnt[e] = run;
-      offsets[e] = run;
-      run += c;
-    }
-    cnt[E] = run;
-    offsets[E] = run;
-  }
+  const int p = blockIdx.x * 256 + threadIdx.x;
+  if (p < npairs) atomicAdd(&hist[idx[p]], 1);
   __syncthreads();
-  for (int e = warp; e < E; e += nw) {
-    int base = cnt[e];
-    for (int p0 = 0; p0 < npairs; p0 += 32) {
-      const int p = p0 + lane;
-      const bool hit = p < npairs && idx[p] == e;
-      const unsigned mask = __ballot_sync(0xffffffffu, hit);
-      if (hit) {
-        const int slot = base + __popc(mask & ((1u << lane) - 1u));
-        slot_token[slot] = p / top;
-        pair_slot[p] = slot;
-      }
-      base += __popc(mask);
-    }
+  for (int e = threadIdx.x; e < E; e += 256)
+    if (hist[e]) atomicAdd(&counts[e], hist[e]);
+}
+__global__ void route_scan_kernel(int* __restrict__ counts, int E, int32_t* __restrict__ offsets, int* __restrict__ cursor) {
+  pdl_wait();
+  pdl_launch_dependents();
+  if (threadIdx.x != 0) return;
+  int run = 0;
+  for (int e = 0; e < E; ++e) {
+    offsets[e] = run;
+    cursor[e] = run;
+    run += counts[e];
+    counts[e] = 0;  // ready for the next call
   }
+  offsets[E] = run;
+}
+__global__ void __launch_bounds__(256) route_place_kernel(const int32_t* __restrict__ idx, int npairs, int top, int* __restrict__ cursor,
+                                                          int32_t* __restrict__ slot_token, int32_t* __restrict__ pair_slot) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int p = blockIdx.x * 256 + threadIdx.x;
+  if (p >= npairs) return;
+  const int slot = atomicAdd(&cursor[idx[p]], 1);
+  slot_token[slot] = p / top;
+  pair_slot[p] = slot;
 }
 
 __global__ void __launch_bounds__(128) route_combine_kernel(float* __restrict__ h, const float* __restrict__ mix, const float* __restrict__ y,
@@ -157,9 +162,9 @@ int launch_route(const void* x, int x_f32, const float* router, const float* cor
   B2_REQUIRE(g.keep >= 1 && g.keep <= g.groups, "route: keep %d outside [1, %d]", g.keep, g.groups);
   B2_REQUIRE(g.top >= 1 && g.top <= g.keep * (g.experts / g.groups), "route: top %d exceeds the %d experts of the kept groups", g.top,
              g.keep * (g.experts / g.groups));
-  const size_t smem = (size_t)RT_WARPS * 2 * g.experts * sizeof(float);
-  B2_REQUIRE(smem <= 48 * 1024, "route: %d experts need %zu bytes of shared memory", g.experts, smem);
-  const dim3 grid((T + RT_WARPS - 1) / RT_WARPS);
+  const size_t smem = ((size_t)2 * g.experts + W) * sizeof(float);
+  B2_REQUIRE(smem <= 48 * 1024, "route: %d experts and width %d need %zu bytes of shared memory", g.experts, W, smem);
+  const dim3 grid(T);
   if (x_f32)
     B2_CUDA_OK(b2_launch(route_kernel<float>, grid, dim3(RT_WARPS * 32), smem, s, (const float*)x, router, correction, g, idx, weight, T, W));
   else
@@ -167,12 +172,17 @@ int launch_route(const void* x, int x_f32, const float* router, const float* cor
   return 0;
 }
 
-int launch_route_permute(const int32_t* idx, int T, int top, int experts, int32_t* offsets, int32_t* slot_token, int32_t* pair_slot,
-                         cudaStream_t s) {
+int launch_route_permute(const int32_t* idx, int T, int top, int experts, int32_t* offsets, int stride, int32_t* slot_token,
+                         int32_t* pair_slot, cudaStream_t s) {
   if (T <= 0) return 0;
-  const int threads = std::min(1024, std::max(32, experts * 32));
-  B2_CUDA_OK(b2_launch(route_permute_kernel, dim3(1), dim3(threads), (size_t)(experts + 1) * sizeof(int), s, idx, T * top, top, experts, offsets,
-                       slot_token, pair_slot));
+  B2_REQUIRE(stride >= experts + 1, "route_permute: stride %d < experts + 1", stride);
+  int* counts = offsets + stride;   // zero between calls (the scan step clears what the histogram added)
+  int* cursor = counts + stride;
+  const int npairs = T * top;
+  B2_REQUIRE((size_t)experts * sizeof(int) <= 48 * 1024, "route_permute: %d experts", experts);
+  B2_CUDA_OK(b2_launch(route_count_kernel, dim3((npairs + 255) / 256), dim3(256), (size_t)experts * sizeof(int), s, idx, npairs, experts, counts));
+  B2_CUDA_OK(b2_launch(route_scan_kernel, dim3(1), dim3(32), 0, s, counts, experts, offsets, cursor));
+  B2_CUDA_OK(b2_launch(route_place_kernel, dim3((npairs + 255) / 256), dim3(256), 0, s, idx, npairs, top, cursor, slot_token, pair_slot));
   return 0;
 }
 
