@@ -254,6 +254,7 @@ __global__ void __launch_bounds__(MA_THREADS, 1) latent_attention_mma_kernel(Mma
   float* row_m = reinterpret_cast<float*>(Ps + MA_ROWS * 72);  // [64]
   float* row_l = row_m + MA_ROWS;                            // [64]
   int* row_pos = reinterpret_cast<int*>(row_l + MA_ROWS);    // [64]
+  int* key_row = row_pos + MA_ROWS;                          // [64] cache rows of the staged keys
   float* Os = reinterpret_cast<float*>(smraw);               // after the sweeps: [64][R16 + 4] over Qs / Ks
 
   int q_row0, q_pos0, nrows, bt_row;
@@ -280,6 +281,7 @@ __global__ void __launch_bounds__(MA_THREADS, 1) latent_attention_mma_kernel(Mma
     const bool live = row < total;
     const int tok = live ? row / g.heads : 0, head = live ? row - tok * g.heads : 0;
     const size_t base = (size_t)(q_row0 + tok) * g.heads + head;
+#pragma unroll 4
     for (int d = lane; d < DP; d += 32) {
       float v = 0.f;
       if (live && d < D) v = d < R ? a.q_abs[base * R + d] : a.q_rot[base * g.rot_dim + (d - R)];
@@ -297,18 +299,27 @@ __global__ void __launch_bounds__(MA_THREADS, 1) latent_attention_mma_kernel(Mma
   const bool vec = (D % 8 == 0);
   auto load_keys = [&](int k0) {
     __syncthreads();  // the previous tile's reads of Ks / Ss / Ps are done
+    // cache row of every key of the tile first (one block-table lookup per key), so that the copies below are independent loads
+    if (tid < MA_KEYS) {
+      const int kp = k0 + tid;
+      key_row[tid] = kp <= max_pos ? bt[kp / a.block_size] * a.block_size + kp % a.block_size : -1;
+    }
+    __syncthreads();
     if (vec) {
       const int cpr = D / 8;  // 16-byte chunks per key row
+#pragma unroll 8
       for (int idx = tid; idx < MA_KEYS * cpr; idx += MA_THREADS) {
-        const int j = idx / cpr, c = idx - j * cpr, kp = k0 + j;
+        const int j = idx / cpr, c = idx - j * cpr;
+        const int kr = key_row[j];
         uint4 v = make_uint4(0, 0, 0, 0);
-        if (kp <= max_pos) v = ld_stream(a.cache + ((size_t)bt[kp / a.block_size] * a.block_size + kp % a.block_size) * D + c * 8);
+        if (kr >= 0) v = ld_stream(a.cache + (size_t)kr * D + c * 8);
         *reinterpret_cast<uint4*>(Ks + j * DP + c * 8) = v;
       }
     } else {
       for (int idx = tid; idx < MA_KEYS * D; idx += MA_THREADS) {
-        const int j = idx / D, d = idx - j * D, kp = k0 + j;
-        Ks[j * DP + d] = kp <= max_pos ? a.cache[((size_t)bt[kp / a.block_size] * a.block_size + kp % a.block_size) * D + d] : __float2bfloat16_rn(0.f);
+        const int j = idx / D, d = idx - j * D;
+        const int kr = key_row[j];
+        Ks[j * DP + d] = kr >= 0 ? a.cache[(size_t)kr * D + d] : __float2bfloat16_rn(0.f);
       }
     }
     __syncthreads();
@@ -355,10 +366,14 @@ __global__ void __launch_bounds__(MA_THREADS, 1) latent_attention_mma_kernel(Mma
     for (int j = 0; j < NF; ++j) wmma::fill_fragment(oacc[i][j], 0.f);
   float mysum = 0.f;
   const int col0 = warp * NF * 16;
+  const bool one_tile = t_hi - t_lo == 1;   // a decode split: the tile of the first sweep and its scores are still staged
+  if (one_tile) __syncthreads();            // publishes row_m
   for (int t = t_lo; t < t_hi; ++t) {
     const int k0 = t * MA_KEYS;
-    load_keys(k0);   // its first barrier also publishes row_m
-    scores();
+    if (!one_tile) {
+      load_keys(k0);   // its first barrier also publishes row_m
+      scores();
+    }
     const int lim = row_pos[r4] - k0;
     const float m = row_m[r4];
     for (int j = q4 * 16; j < q4 * 16 + 16; ++j) {
@@ -450,7 +465,7 @@ __global__ void __launch_bounds__(128) latent_merge_kernel(const float* __restri
 
 size_t mma_attn_smem(const LatentGeom& g) {
   const int D = g.kv_rank + g.rot_dim, DP = ((D + 15) & ~15) + 8;
-  return (size_t)2 * MA_ROWS * DP * 2 + (size_t)MA_ROWS * 68 * 4 + (size_t)MA_ROWS * 72 * 2 + 3 * MA_ROWS * 4;
+  return (size_t)2 * MA_ROWS * DP * 2 + (size_t)MA_ROWS * 68 * 4 + (size_t)MA_ROWS * 72 * 2 + 4 * MA_ROWS * 4;
 }
 
 template <int NF>

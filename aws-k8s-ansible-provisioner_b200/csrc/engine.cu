@@ -853,6 +853,28 @@ int forward_list(b2_engine* e, int T, int ntiles, int nlast) {
   }
   dbg(0);
   const PrefillTile* tiles = ntiles > 0 ? e->d_tiles : nullptr;
+  // C (fp32 [M][N]) = A (operand type [M][K]) . Wt^T.  Prompt-sized bf16 products whose K the tcgen05 projection kernel can
+  // tile (gemm_tc.cu: TMA needs 16-byte rows, its k-block is 64) take that kernel, fp32 sums written directly; everything else
+  // -- decode steps, fp32 mode, odd shapes -- takes gemm_any.cu.
+  static const bool use_tc = [] { const char* v = getenv("B2_LIST_TC"); return !(v && *v == '0'); }();
+  auto dense = [&](const void* A, const void* Wt, float* C, int M, int N, int K, float alpha) -> int {
+    if (use_tc && !f && alpha == 1.f && M > 64 && N >= 128 && K % 64 == 0) {
+      TcGemmArgs a;
+      a.bn = tc_pick_bn(M);
+      B2_TRY(b2_make_tmap_bf16(&a.tmap_w, Wt, (uint64_t)N, (uint64_t)K, (uint64_t)K, 128));
+      B2_TRY(b2_make_tmap_bf16(&a.tmap_x, A, (uint64_t)M, (uint64_t)K, (uint64_t)K, (uint32_t)a.bn));
+      a.T = M; a.N = N; a.K = K;
+      a.nsplit = 1;
+      a.out = C;
+      a.x_raw = A;
+      a.argmax_packed = nullptr;
+      a.epilogue = TC_EPI_F32_PARTIAL;
+      return launch_linear_tc(a, st);
+    }
+    AnyGemm a;
+    a.A = A; a.W = Wt; a.C = C; a.M = M; a.N = N; a.K = K; a.lda = K; a.ldw = K; a.ldc = N; a.alpha = alpha;
+    return launch_gemm_any(a, f, f, 1, 1, 0, st);
+  };
   for (int l = 0; l < c.num_layers; ++l) {
     ListLayer& L = e->ll[l];
     const b2_layer_spec& sp = L.sp;
@@ -867,9 +889,7 @@ int forward_list(b2_engine* e, int T, int ntiles, int nlast) {
     }
     {
       KL k(e, B2K_GEMM_QKV);  // q of every head and, for a layer with its own latent, the latent and the shared key piece: one projection
-      AnyGemm a;
-      a.A = e->l_x1; a.W = L.wqd; a.C = e->l_qd; a.M = T; a.N = L.nqd; a.K = W; a.lda = W; a.ldw = W; a.ldc = L.nqd;
-      if (!k.skip()) B2_TRY(launch_gemm_any(a, f, f, 1, 1, 0, st));
+      if (!k.skip()) B2_TRY(dense(e->l_x1, L.wqd, e->l_qd, T, L.nqd, W, 1.f));
     }
     {
       KL k(e, B2K_ROPE_KV);
@@ -899,9 +919,7 @@ int forward_list(b2_engine* e, int T, int ntiles, int nlast) {
     }
     {
       KL k(e, B2K_GEMM_O);
-      AnyGemm a;
-      a.A = e->l_av; a.W = L.wo; a.C = e->l_mix; a.M = T; a.N = W; a.K = sp.heads * sp.vdim; a.lda = a.K; a.ldw = a.K; a.ldc = W;
-      if (!k.skip()) B2_TRY(launch_gemm_any(a, f, f, 1, 1, 0, st));
+      if (!k.skip()) B2_TRY(dense(e->l_av, L.wo, e->l_mix, T, W, sp.heads * sp.vdim, 1.f));
     }
     if (has_ff) {
       RouteGeom rg{sp.experts, sp.top, sp.groups, sp.groups_keep};
@@ -914,7 +932,7 @@ int forward_list(b2_engine* e, int T, int ntiles, int nlast) {
         if (!k.skip()) B2_TRY(launch_route_permute(e->l_idx, T, sp.top, sp.experts, e->l_offsets, e->l_offsets_stride, e->l_slot_token, e->l_pair_slot, st));
       }
       const int max_tiles = std::min(e->l_tiles_cap, (T * sp.top + any_gemm_tile_rows() - 1) / any_gemm_tile_rows() + sp.experts);
-      {
+      if (T * sp.top > any_gemm_ragged_rows_limit() || W > 16384 || sp.ff_dim > 16384) {   // (a decode-sized step streams the experts' weights group by group instead)
         KL k(e, B2K_MISC);
         if (!k.skip()) B2_TRY(launch_ragged_tiles(e->l_offsets, sp.experts, e->l_tile_group, e->l_tile_row0, e->l_ntiles, max_tiles, st));
       }
@@ -945,10 +963,7 @@ int forward_list(b2_engine* e, int T, int ntiles, int nlast) {
   }
   {
     KL k(e, B2K_LMHEAD);
-    AnyGemm a;
-    a.A = e->l_xl; a.W = e->l_head; a.C = e->l_logits; a.M = nlast; a.N = c.vocab; a.K = W; a.lda = W; a.ldw = W; a.ldc = c.vocab;
-    a.alpha = c.logit_scale != 0.f ? c.logit_scale : 1.f;
-    if (!k.skip()) B2_TRY(launch_gemm_any(a, f, f, 1, 1, 0, st));
+    if (!k.skip()) B2_TRY(dense(e->l_xl, e->l_head, e->l_logits, nlast, c.vocab, W, c.logit_scale != 0.f ? c.logit_scale : 1.f));
   }
   {
     KL k(e, B2K_MISC);

@@ -396,6 +396,11 @@ __global__ void ragged_tiles_kernel(const int* __restrict__ group_offsets, int G
 }  // namespace
 
 int any_gemm_tile_rows() { return BM; }
+// ragged launches with at most this many rows in all groups together stream the weights and need no tile list
+int any_gemm_ragged_rows_limit() {
+  static const bool use_rows = [] { const char* e = getenv("B2_ANY_ROWS"); return !(e && *e == '0'); }();
+  return use_rows ? 8 * RB : 0;
+}
 
 int launch_ragged_tiles(const int* group_offsets, int G, int* tile_group, int* tile_row0, int* n_tiles, int cap, cudaStream_t s) {
   B2_CUDA_OK(b2_launch(ragged_tiles_kernel, dim3(1), dim3(32), 0, s, group_offsets, G, tile_group, tile_row0, n_tiles, cap));
@@ -408,7 +413,7 @@ int launch_gemm_any(const AnyGemm& g, int a_f32, int w_f32, int c_f32, int batch
   {  // few rows: stream the weights (rows of every group counted together for the ragged form: they bound the work per group)
     static const bool use_rows = [] { const char* e = getenv("B2_ANY_ROWS"); return !(e && *e == '0'); }();
     const bool ragged = g.tile_group != nullptr;
-    const bool few = ragged ? (ragged_rows > 0 && ragged_rows <= 8 * RB && groups > 0) : (g.M > 0 && g.M <= 4 * RB);
+    const bool few = (ragged ? (ragged_rows > 0 && ragged_rows <= 8 * RB && groups > 0) : (g.M > 0 && g.M <= 4 * RB)) && g.K <= 16384;
     if (use_rows && few && a_f32 == w_f32) {
       int rc = 1;
       if (a_f32 && c_f32) rc = launch_rows<float, float, float>(g, ragged ? groups : 0, batch, s);

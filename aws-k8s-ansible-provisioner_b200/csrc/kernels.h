@@ -232,6 +232,7 @@ struct AnyGemm {
   float alpha = 1.f;
 };
 int any_gemm_tile_rows();
+int any_gemm_ragged_rows_limit();
 int launch_ragged_tiles(const int* group_offsets, int G, int* tile_group, int* tile_row0, int* n_tiles, int cap, cudaStream_t s);
 // *_f32: element type of A / W / C (1 = fp32, 0 = bf16); batch: strided batches (dense); max_tiles: capacity of the tile list (ragged);
 // ragged_rows / groups: total rows over all groups and the number of groups (ragged), which let a launch with few rows take the

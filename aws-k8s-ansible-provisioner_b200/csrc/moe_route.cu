@@ -140,6 +140,37 @@ __global__ void __launch_bounds__(256) route_place_kernel(const int32_t* __restr
   pair_slot[p] = slot;
 }
 
+// few pairs (a decode step): the three steps in one CTA, histogram and cursors in shared memory
+__global__ void __launch_bounds__(1024) route_permute_small_kernel(const int32_t* __restrict__ idx, int npairs, int top, int E,
+                                                                   int32_t* __restrict__ offsets, int32_t* __restrict__ slot_token,
+                                                                   int32_t* __restrict__ pair_slot) {
+  extern __shared__ int cur[];  // [E]
+  pdl_wait();
+  pdl_launch_dependents();
+  for (int e = threadIdx.x; e < E; e += 1024) cur[e] = 0;
+  __syncthreads();
+  const int p = threadIdx.x;
+  const int mine = p < npairs ? idx[p] : -1;
+  if (mine >= 0) atomicAdd(&cur[mine], 1);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int run = 0;
+    for (int e = 0; e < E; ++e) {
+      const int c = cur[e];
+      offsets[e] = run;
+      cur[e] = run;
+      run += c;
+    }
+    offsets[E] = run;
+  }
+  __syncthreads();
+  if (mine >= 0) {
+    const int slot = atomicAdd(&cur[mine], 1);
+    slot_token[slot] = p / top;
+    pair_slot[p] = slot;
+  }
+}
+
 __global__ void __launch_bounds__(128) route_combine_kernel(float* __restrict__ h, const float* __restrict__ mix, const float* __restrict__ y,
                                                             const float* __restrict__ weight, const int32_t* __restrict__ pair_slot, int W,
                                                             int top) {
@@ -180,6 +211,11 @@ int launch_route_permute(const int32_t* idx, int T, int top, int experts, int32_
   int* cursor = counts + stride;
   const int npairs = T * top;
   B2_REQUIRE((size_t)experts * sizeof(int) <= 48 * 1024, "route_permute: %d experts", experts);
+  if (npairs <= 1024) {
+    B2_CUDA_OK(b2_launch(route_permute_small_kernel, dim3(1), dim3(1024), (size_t)experts * sizeof(int), s, idx, npairs, top, experts, offsets,
+                         slot_token, pair_slot));
+    return 0;
+  }
   B2_CUDA_OK(b2_launch(route_count_kernel, dim3((npairs + 255) / 256), dim3(256), (size_t)experts * sizeof(int), s, idx, npairs, experts, counts));
   B2_CUDA_OK(b2_launch(route_scan_kernel, dim3(1), dim3(32), 0, s, counts, experts, offsets, cursor));
   B2_CUDA_OK(b2_launch(route_place_kernel, dim3((npairs + 255) / 256), dim3(256), 0, s, idx, npairs, top, cursor, slot_token, pair_slot));
