@@ -278,16 +278,20 @@ __global__ void __launch_bounds__(MA_THREADS, 1) latent_attention_mma_kernel(Mma
   // ---- stage Q (bf16), zero the padding columns of both operand slabs ----
   for (int r = warp; r < MA_ROWS; r += MA_THREADS / 32) {
     const int row = first + r, lane = tid & 31;
-    const bool live = row < total;
-    const int tok = live ? row / g.heads : 0, head = live ? row - tok * g.heads : 0;
-    const size_t base = (size_t)(q_row0 + tok) * g.heads + head;
+    if (row < total) {
+      const int tok = row / g.heads, head = row - tok * g.heads;
+      const size_t base = (size_t)(q_row0 + tok) * g.heads + head;
+      const float* qa = a.q_abs + base * R;
+      const float* qr = a.q_rot + base * g.rot_dim;
 #pragma unroll 4
-    for (int d = lane; d < DP; d += 32) {
-      float v = 0.f;
-      if (live && d < D) v = d < R ? a.q_abs[base * R + d] : a.q_rot[base * g.rot_dim + (d - R)];
-      Qs[r * DP + d] = __float2bfloat16_rn(v);
-      Ks[r * DP + d] = __float2bfloat16_rn(0.f);
+      for (int d = lane; d < R; d += 32) Qs[r * DP + d] = __float2bfloat16_rn(qa[d]);
+      for (int d = lane; d < g.rot_dim; d += 32) Qs[r * DP + R + d] = __float2bfloat16_rn(qr[d]);
+      for (int d = D + lane; d < DP; d += 32) Qs[r * DP + d] = __float2bfloat16_rn(0.f);
+    } else {   // rows past the block's last: zeros, 16 bytes at a time (DP is a multiple of 8)
+      for (int c = lane; c < DP / 8; c += 32) *reinterpret_cast<uint4*>(Qs + r * DP + c * 8) = make_uint4(0, 0, 0, 0);
     }
+    // key slab: only the padding columns need zeros (the copies write [0, D) of every row, zeros past the last key)
+    for (int d = D + lane; d < DP; d += 32) Ks[r * DP + d] = __float2bfloat16_rn(0.f);
   }
   if (tid < MA_ROWS) {
     const int row = first + tid;
@@ -433,33 +437,34 @@ __global__ void __launch_bounds__(MA_THREADS, 1) latent_attention_mma_kernel(Mma
   }
 }
 
-// folds the splits of every (token, head) row and the sink into the output; one warp per row
+// folds the splits of every (token, head) row and the sink into the output; one CTA per row, thread d owns latent dims d, d + 128, ...
 __global__ void __launch_bounds__(128) latent_merge_kernel(const float* __restrict__ partial, int nsplit, int R, int heads,
                                                            const int32_t* __restrict__ seq_lens, const float* __restrict__ sink,
                                                            bf16* __restrict__ out_lat, int nrows) {
+  __shared__ float w_s[32];
+  __shared__ float inv_s;
   pdl_wait();
   pdl_launch_dependents();
-  const int row = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-  if (row >= nrows) return;
+  const int row = blockIdx.x, lane = threadIdx.x & 31;
   const int tok = row / heads, head = row - tok * heads;
   if (seq_lens != nullptr && seq_lens[tok] <= 0) return;
   const float* p = partial + (size_t)row * nsplit * (R + 2);
-  const float sk = sink[head];
-  // lane s holds split s (nsplit <= 32): its maximum, then its weight exp(m_s - m)
-  const float m_s = lane < nsplit ? p[(size_t)lane * (R + 2)] : -INFINITY;
-  const float l_s = lane < nsplit ? p[(size_t)lane * (R + 2) + 1] : 0.f;
-  const float mf = fmaxf(warp_max(m_s), sk);
-  const float w_s = m_s == -INFINITY ? 0.f : expf(m_s - mf);
-  const float inv = 1.0f / (warp_sum(l_s * w_s) + expf(sk - mf));
-  for (int d0 = 0; d0 < R; d0 += 32) {
-    const int d = d0 + lane;
+  if (threadIdx.x < 32) {   // lane s holds split s (nsplit <= 32): its maximum, then its weight exp(m_s - m)
+    const float sk = sink[head];
+    const float m = lane < nsplit ? p[(size_t)lane * (R + 2)] : -INFINITY;
+    const float l = lane < nsplit ? p[(size_t)lane * (R + 2) + 1] : 0.f;
+    const float mf = fmaxf(warp_max(m), sk);
+    const float w = m == -INFINITY ? 0.f : expf(m - mf);
+    const float den = warp_sum(l * w) + expf(sk - mf);
+    w_s[lane] = w;
+    if (lane == 0) inv_s = 1.0f / den;
+  }
+  __syncthreads();
+  for (int d = threadIdx.x; d < R; d += 128) {
     float acc = 0.f;
-#pragma unroll 4
-    for (int s = 0; s < nsplit; ++s) {
-      const float w = __shfl_sync(0xffffffffu, w_s, s);
-      if (d < R && w != 0.f) acc = fmaf(p[(size_t)s * (R + 2) + 2 + d], w, acc);
-    }
-    if (d < R) out_lat[(size_t)row * R + d] = __float2bfloat16_rn(acc * inv);
+#pragma unroll 8
+    for (int s = 0; s < nsplit; ++s) acc = fmaf(p[(size_t)s * (R + 2) + 2 + d], w_s[s], acc);
+    out_lat[(size_t)row * R + d] = __float2bfloat16_rn(acc * inv_s);
   }
 }
 
@@ -535,7 +540,7 @@ int launch_latent_finish(const float* qd, int ld, const LatentGeom& g, int has_k
 }
 
 size_t latent_attention_scratch_floats(int max_rows, int max_heads, int max_rank) {
-  // decode steps cut the keys into splits until about two CTAs per SM exist; every (row block, split) leaves 64 rows
+  // decode steps cut the keys into splits until every SM has a CTA; every (row block, split) leaves up to 64 rows
   return ((size_t)2 * 148 + (size_t)max_rows * ((max_heads + MA_ROWS - 1) / MA_ROWS)) * MA_ROWS * ((size_t)max_rank + 2);
 }
 
@@ -552,7 +557,7 @@ int launch_latent_attention(const float* q_abs, const float* q_rot, const void* 
     const int blocks_y = ((tiles != nullptr ? 64 : 1) * g.heads + MA_ROWS - 1) / MA_ROWS;
     const int blocks = (tiles != nullptr ? ntiles : T) * blocks_y;
     if (tiles == nullptr && scratch != nullptr) {   // decode: few rows, long caches -> cut the keys
-      int ns = (2 * 148) / std::max(blocks, 1);
+      int ns = 148 / std::max(blocks, 1);   // one CTA per SM fits (the operand slabs fill its shared memory): one wave
       ns = std::min(std::min(ns, 32), std::max(1, (max_context + MA_KEYS - 1) / MA_KEYS));
       while (ns > 1 && (size_t)T * g.heads * ns * (g.kv_rank + 2) > scratch_floats) --ns;
       a.nsplit = std::max(ns, 1);
@@ -563,7 +568,7 @@ int launch_latent_attention(const float* q_abs, const float* q_rot, const void* 
     else if (nf == 2) B2_TRY_RC(launch_mma<2>(a, grid, mma_smem, s));
     else B2_TRY_RC(launch_mma<4>(a, grid, mma_smem, s));
     if (a.nsplit > 1)
-      B2_CUDA_OK(b2_launch(latent_merge_kernel, dim3((T * g.heads + 3) / 4), dim3(128), 0, s, (const float*)scratch, a.nsplit, g.kv_rank, g.heads,
+      B2_CUDA_OK(b2_launch(latent_merge_kernel, dim3(T * g.heads), dim3(128), 0, s, (const float*)scratch, a.nsplit, g.kv_rank, g.heads,
                            seq_lens, sink, (bf16*)out_lat, T * g.heads));
     return 0;
   }

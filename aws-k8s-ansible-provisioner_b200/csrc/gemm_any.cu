@@ -23,7 +23,7 @@
 // Few rows (a decode step: M <= 64 per batch, or experts that see a handful of tokens each) take gemm_any_rows_kernel
 // instead: the product is then a stream of weights, not arithmetic.  The rows are staged in shared memory once per CTA,
 // every warp walks two weight rows at a time with 16-byte loads (eight in flight per lane) and keeps one accumulator per
-// staged row; a CTA covers 8 weight rows, so N / 8 CTAs (times batches or experts) pull on HBM at once.
+// staged row; a CTA covers 8 to 64 weight rows (8 while that still leaves every SM several CTAs).
 #include <mma.h>
 
 #include "kernels.h"
@@ -232,7 +232,7 @@ __global__ void __launch_bounds__(128) gemm_any_mma_kernel(AnyGemm g) {
 }
 
 // ---- few rows: weight-streaming form ----
-constexpr int RB = 16, ROWS_NPB = 8;   // staged rows per pass; weight rows per CTA (4 warps x one pair)
+constexpr int RB = 16, ROWS_NPB = 8;   // staged rows per pass; fewest weight rows per CTA (4 warps x one pair)
 
 template <typename T>
 __device__ __forceinline__ void load8(const T* p, int k, int K, bool vec, float* f);
@@ -256,8 +256,45 @@ __device__ __forceinline__ void load8<float>(const float* p, int k, int K, bool 
   }
 }
 
+// eight weights as they lie in memory (16 or 32 bytes), widened only when they are used: four k-steps of two weight rows stay in
+// flight per lane without holding 64 floats
+template <typename T>
+struct Raw8;
+template <>
+struct Raw8<bf16> {
+  uint4 v;
+  __device__ __forceinline__ void load(const bf16* p, int k, int K, bool vec) {
+    if (vec && k + 8 <= K) v = ld_stream(p + k);
+    else {
+      bf16* e = reinterpret_cast<bf16*>(&v);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) e[j] = k + j < K ? p[k + j] : __float2bfloat16_rn(0.f);
+    }
+  }
+  __device__ __forceinline__ void widen(float* f) const { unpack8(v, f); }
+};
+template <>
+struct Raw8<float> {
+  float4 a, b;
+  __device__ __forceinline__ void load(const float* p, int k, int K, bool vec) {
+    if (vec && k + 8 <= K) {
+      a = *reinterpret_cast<const float4*>(p + k);
+      b = *reinterpret_cast<const float4*>(p + k + 4);
+    } else {
+      float f[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) f[j] = k + j < K ? p[k + j] : 0.f;
+      a = make_float4(f[0], f[1], f[2], f[3]);
+      b = make_float4(f[4], f[5], f[6], f[7]);
+    }
+  }
+  __device__ __forceinline__ void widen(float* f) const {
+    f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+  }
+};
+
 template <typename TA, typename TW, typename TC>
-__global__ void __launch_bounds__(128) gemm_any_rows_kernel(AnyGemm g, int rows_per_pass) {
+__global__ void __launch_bounds__(128) gemm_any_rows_kernel(AnyGemm g, int rows_per_pass, int npb) {
   extern __shared__ __align__(16) unsigned char rows_smem[];   // [rows_per_pass][Kp] of TA, Kp = K rounded up to 8
   TA* As = reinterpret_cast<TA*>(rows_smem);
   pdl_wait();
@@ -282,7 +319,7 @@ __global__ void __launch_bounds__(128) gemm_any_rows_kernel(AnyGemm g, int rows_
   const int K = g.K, Kp = (K + 7) & ~7;
   const bool a_vec = (g.lda % 8 == 0) && ((reinterpret_cast<uintptr_t>(A) & 31) == 0);
   const bool w_vec = (g.ldw % 8 == 0) && ((reinterpret_cast<uintptr_t>(W) & 31) == 0);
-  const int n_base = blockIdx.x * ROWS_NPB;
+  const int n_base = blockIdx.x * npb;
   for (int r0 = row_lo; r0 < row_hi; r0 += rows_per_pass) {
     const int rb = min(rows_per_pass, row_hi - r0);
     __syncthreads();
@@ -299,8 +336,8 @@ __global__ void __launch_bounds__(128) gemm_any_rows_kernel(AnyGemm g, int rows_
       }
     }
     __syncthreads();
-    {   // this warp's pair of weight rows
-      const int n = n_base + warp * 2;
+    for (int pi = 0; pi < npb / 8; ++pi) {   // this warp's pairs of weight rows
+      const int n = n_base + warp * (npb / 4) + pi * 2;
       if (n < g.N) {
         const bool two = n + 1 < g.N;
         const TW* w0 = W + (long)n * g.ldw;
@@ -308,26 +345,33 @@ __global__ void __launch_bounds__(128) gemm_any_rows_kernel(AnyGemm g, int rows_
         float acc[2 * RB];   // [m] row n, [RB + m] row n + 1
 #pragma unroll
         for (int m = 0; m < 2 * RB; ++m) acc[m] = 0.f;
-        float f0[8], f1[8], g0[8], g1[8];
-        int k = lane * 8;
-        if (k < Kp) { load8<TW>(w0, k, K, w_vec, f0); load8<TW>(w1, k, K, w_vec, f1); }
-        for (; k < Kp; k += 256) {
-          const int kn = k + 256;
-          if (kn < Kp) { load8<TW>(w0, kn, K, w_vec, g0); load8<TW>(w1, kn, K, w_vec, g1); }   // next step's weights are in flight
+        for (int kb = lane * 8; kb < Kp; kb += 4 * 256) {   // four k-steps of both rows in flight
+          Raw8<TW> r0[4], r1[4];
 #pragma unroll
-          for (int m = 0; m < RB; ++m) {
-            if (m < rb) {
-              float fa[8];
-              load8<TA>(As + (size_t)m * Kp, k, Kp, true, fa);
+          for (int u = 0; u < 4; ++u) {
+            const int k = kb + u * 256;
+            if (k < Kp) { r0[u].load(w0, k, K, w_vec); r1[u].load(w1, k, K, w_vec); }
+          }
 #pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                acc[m] = fmaf(fa[j], f0[j], acc[m]);
-                acc[RB + m] = fmaf(fa[j], f1[j], acc[RB + m]);
+          for (int u = 0; u < 4; ++u) {
+            const int k = kb + u * 256;
+            if (k >= Kp) break;
+            float f0[8], f1[8];
+            r0[u].widen(f0);
+            r1[u].widen(f1);
+#pragma unroll
+            for (int m = 0; m < RB; ++m) {
+              if (m < rb) {
+                float fa[8];
+                load8<TA>(As + (size_t)m * Kp, k, Kp, true, fa);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                  acc[m] = fmaf(fa[j], f0[j], acc[m]);
+                  acc[RB + m] = fmaf(fa[j], f1[j], acc[RB + m]);
+                }
               }
             }
           }
-#pragma unroll
-          for (int j = 0; j < 8; ++j) { f0[j] = g0[j]; f1[j] = g1[j]; }
         }
         // 32 sums over 32 lanes in 31 shuffles: each round halves the values a lane holds; lane L ends with value L
 #pragma unroll
@@ -372,8 +416,134 @@ int launch_rows(const AnyGemm& g, int groups, int batch, cudaStream_t s) {
     static B2PerDeviceOnce once;
     if (once.need()) B2_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
   }
-  const dim3 grid((g.N + ROWS_NPB - 1) / ROWS_NPB, groups > 0 ? groups : 1, groups > 0 ? 1 : (batch > 0 ? batch : 1));
-  B2_CUDA_OK(b2_launch(kern, grid, dim3(128), smem, s, g, rpp));
+  // weight rows per CTA: eight (one pair per warp) while that still gives every SM a few CTAs, more for wide outputs so that
+  // the staged rows are reused
+  const int other = groups > 0 ? groups : (batch > 0 ? batch : 1);
+  int npb = ROWS_NPB;
+  while (npb < 64 && (long)((g.N + 2 * npb - 1) / (2 * npb)) * other >= 4 * 148) npb *= 2;
+  const dim3 grid((g.N + npb - 1) / npb, groups > 0 ? groups : 1, groups > 0 ? 1 : (batch > 0 ? batch : 1));
+  B2_CUDA_OK(b2_launch(kern, grid, dim3(128), smem, s, g, rpp, npb));
+  return 0;
+}
+
+// ---- few rows, bf16 operands: the weight stream on warp-level MMAs ----
+// Above a handful of staged rows the plain-FMA form is bound by its multiply-adds, not by HBM (16 rows cost 256 FMAs per
+// 32 weight bytes a lane loads).  Here the weights are the 16 x 16 operand of mma.m16n8k16 and eight token rows the 16 x 8
+// one, both loaded from global memory straight into fragment registers with 16-byte loads: inside a 32-wide k chunk lane
+// (g, c) = (lane / 4, lane % 4) takes elements [8c, 8c + 8) of weight rows g and g + 8 and of token row g.  An MMA does
+// not care which physical k sits behind its logical k as long as both operands agree, so elements 0..3 of the eight feed
+// one MMA (logical k 2c, 2c + 1, 2c + 8, 2c + 9) and elements 4..7 the next.  A CTA owns 16 weight rows; its four warps
+// take interleaved k chunks (so a weight row is read in 256-byte runs) and their partial tiles are summed in warp order
+// through shared memory.  Token rows are re-read by every CTA from L1/L2; the weights are streamed past L1.
+__device__ __forceinline__ void mma_16816(float* d, unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0, unsigned b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// NT: eight-row token tiles per pass (rows per pass = 8 * NT); U: k chunks in flight per warp
+template <typename TC, int NT, int U>
+__global__ void __launch_bounds__(128) gemm_any_rows_mma_kernel(AnyGemm g) {
+  __shared__ float red[4][NT][32][4];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, gq = lane >> 2, c = lane & 3;
+  const bf16* A = reinterpret_cast<const bf16*>(g.A);
+  const bf16* W = reinterpret_cast<const bf16*>(g.W);
+  TC* C = reinterpret_cast<TC*>(g.C);
+  int row_lo, row_hi;
+  if (g.group_offsets != nullptr) {   // ragged: blockIdx.y = group
+    row_lo = g.group_offsets[blockIdx.y];
+    row_hi = g.group_offsets[blockIdx.y + 1];
+    if (row_lo >= row_hi) return;
+    W += (size_t)blockIdx.y * g.w_bs;
+  } else {
+    row_lo = 0;
+    row_hi = g.M;
+    A += (size_t)blockIdx.z * g.a_bs;
+    W += (size_t)blockIdx.z * g.w_bs;
+    C += (size_t)blockIdx.z * g.c_bs;
+  }
+  const int K = g.K, n0 = blockIdx.x * 16;
+  const bf16* w_lo = W + (long)min(n0 + gq, g.N - 1) * g.ldw + c * 8;       // rows past N are read again and dropped at the store
+  const bf16* w_hi = W + (long)min(n0 + gq + 8, g.N - 1) * g.ldw + c * 8;
+  const int nchunk = (K + 31) >> 5;
+  for (int r0 = row_lo; r0 < row_hi; r0 += 8 * NT) {
+    const bf16* tok[NT];
+#pragma unroll
+    for (int t = 0; t < NT; ++t) {
+      const int r = r0 + t * 8 + gq;
+      tok[t] = r < row_hi ? A + (g.a_rows ? (long)g.a_rows[r] : (long)r) * g.lda + c * 8 : nullptr;
+    }
+    float acc[NT][4];
+#pragma unroll
+    for (int t = 0; t < NT; ++t)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc[t][i] = 0.f;
+    for (int ch0 = warp; ch0 < nchunk; ch0 += 4 * U) {
+      uint4 wl[U], wh[U], tv[U][NT];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int k = (ch0 + 4 * u) << 5;
+        const bool in = k + c * 8 < K;   // K is a multiple of 8: a lane's eight elements are inside or outside together
+        wl[u] = in ? ld_stream(w_lo + k) : make_uint4(0, 0, 0, 0);
+        wh[u] = in ? ld_stream(w_hi + k) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+        for (int t = 0; t < NT; ++t)
+          tv[u][t] = (in && tok[t] != nullptr) ? __ldg(reinterpret_cast<const uint4*>(tok[t] + k)) : make_uint4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+#pragma unroll
+        for (int t = 0; t < NT; ++t) {
+          mma_16816(acc[t], wl[u].x, wh[u].x, wl[u].y, wh[u].y, tv[u][t].x, tv[u][t].y);
+          mma_16816(acc[t], wl[u].z, wh[u].z, wl[u].w, wh[u].w, tv[u][t].z, tv[u][t].w);
+        }
+    }
+    __syncthreads();   // the previous pass has read `red`
+#pragma unroll
+    for (int t = 0; t < NT; ++t)
+      *reinterpret_cast<float4*>(&red[warp][t][lane][0]) = make_float4(acc[t][0], acc[t][1], acc[t][2], acc[t][3]);
+    __syncthreads();
+    // fragment element i of lane (g, c): weight row g + 8 * (i / 2), token row 2c + (i % 2)
+    for (int idx = tid; idx < NT * 128; idx += 128) {
+      const int t = idx >> 7, rem = idx & 127, wr = rem & 15, tk = rem >> 4;   // consecutive threads -> consecutive weight rows
+      const int ln = (wr & 7) * 4 + (tk >> 1), i = (wr >> 3) * 2 + (tk & 1);
+      const int r = r0 + t * 8 + tk, n = n0 + wr;
+      if (r >= row_hi || n >= g.N) continue;
+      float v = ((red[0][t][ln][i] + red[1][t][ln][i]) + red[2][t][ln][i]) + red[3][t][ln][i];
+      v *= g.alpha;
+      TC* dst = C + (size_t)r * g.ldc + n;
+      if (g.epilogue == ANY_EPI_RELU2) {
+        v = fmaxf(v, 0.f);
+        v = v * v;
+      }
+      if (g.epilogue == ANY_EPI_ADD) {
+        if constexpr (sizeof(TC) == 4) *dst = (TC)((float)*dst + v);
+      } else {
+        if constexpr (sizeof(TC) == 4) *dst = v;
+        else *dst = __float2bfloat16_rn(v);
+      }
+    }
+  }
+}
+
+// 16-byte fragment loads need K, both row strides and both bases in multiples of 8 elements
+inline bool rows_mma_ok(const AnyGemm& g) {
+  return g.K % 8 == 0 && g.lda % 8 == 0 && g.ldw % 8 == 0 && g.a_bs % 8 == 0 && g.w_bs % 8 == 0 &&
+         (reinterpret_cast<uintptr_t>(g.A) & 15) == 0 && (reinterpret_cast<uintptr_t>(g.W) & 15) == 0;
+}
+
+template <typename TC>
+int launch_rows_mma(const AnyGemm& g, int groups, int batch, cudaStream_t s) {
+  const dim3 grid((g.N + 15) / 16, groups > 0 ? groups : 1, groups > 0 ? 1 : (batch > 0 ? batch : 1));
+  // rows per pass: a ragged group's count is only known on the device (16 covers the usual handful per expert; more rows
+  // take more passes over weights that are then in L2)
+  const int rows = groups > 0 ? 16 : g.M;
+  if (rows <= 8) B2_CUDA_OK(b2_launch(gemm_any_rows_mma_kernel<TC, 1, 4>, grid, dim3(128), 0, s, g));
+  else if (rows <= 16) B2_CUDA_OK(b2_launch(gemm_any_rows_mma_kernel<TC, 2, 4>, grid, dim3(128), 0, s, g));
+  else if (rows <= 32) B2_CUDA_OK(b2_launch(gemm_any_rows_mma_kernel<TC, 4, 2>, grid, dim3(128), 0, s, g));
+  else B2_CUDA_OK(b2_launch(gemm_any_rows_mma_kernel<TC, 8, 1>, grid, dim3(128), 0, s, g));
   return 0;
 }
 
@@ -414,6 +584,9 @@ int launch_gemm_any(const AnyGemm& g, int a_f32, int w_f32, int c_f32, int batch
     static const bool use_rows = [] { const char* e = getenv("B2_ANY_ROWS"); return !(e && *e == '0'); }();
     const bool ragged = g.tile_group != nullptr;
     const bool few = (ragged ? (ragged_rows > 0 && ragged_rows <= 8 * RB && groups > 0) : (g.M > 0 && g.M <= 4 * RB)) && g.K <= 16384;
+    static const bool use_rows_mma = [] { const char* e = getenv("B2_ANY_ROWS_MMA"); return !(e && *e == '0'); }();  // 0: plain FMAs (cross-check)
+    if (use_rows && use_rows_mma && few && !a_f32 && !w_f32 && rows_mma_ok(g))
+      return c_f32 ? launch_rows_mma<float>(g, ragged ? groups : 0, batch, s) : launch_rows_mma<bf16>(g, ragged ? groups : 0, batch, s);
     if (use_rows && few && a_f32 == w_f32) {
       int rc = 1;
       if (a_f32 && c_f32) rc = launch_rows<float, float, float>(g, ragged ? groups : 0, batch, s);

@@ -65,10 +65,10 @@ __global__ void __launch_bounds__(128) unit_norm2_kernel(const float* __restrict
   }
 }
 
-__global__ void __launch_bounds__(256) logits_finish_kernel(const float* __restrict__ logits, int32_t* __restrict__ out_tokens,
+__global__ void __launch_bounds__(1024) logits_finish_kernel(const float* __restrict__ logits, int32_t* __restrict__ out_tokens,
                                                             bf16* __restrict__ lb, int lb_rows, int V, int v_pad) {
-  __shared__ float bv[8];
-  __shared__ int bi[8];
+  __shared__ float bv[32];
+  __shared__ int bi[32];
   pdl_wait();
   pdl_launch_dependents();
   const int r = blockIdx.x;
@@ -76,7 +76,8 @@ __global__ void __launch_bounds__(256) logits_finish_kernel(const float* __restr
   const float* row = logits + (size_t)r * V;
   float best = -INFINITY;
   int besti = 0x7fffffff;
-  for (int i = threadIdx.x; i < v_pad; i += 256) {
+#pragma unroll 4
+  for (int i = threadIdx.x; i < v_pad; i += 1024) {
     const float v = i < V ? row[i] : -INFINITY;
     if (lb != nullptr) lb[(size_t)r * v_pad + i] = __float2bfloat16_rn(v);
     if (i < V && (v > best || (v == best && i < besti))) {
@@ -98,7 +99,7 @@ __global__ void __launch_bounds__(256) logits_finish_kernel(const float* __restr
   }
   __syncthreads();
   if (threadIdx.x == 0) {
-    for (int w = 1; w < 8; ++w)
+    for (int w = 1; w < 32; ++w)
       if (bv[w] > best || (bv[w] == best && bi[w] < besti)) {
         best = bv[w];
         besti = bi[w];
@@ -131,7 +132,7 @@ int launch_unit_norm2(const float* h, const float* gain_a, const float* gain_b, 
 
 int launch_logits_finish(const float* logits, int32_t* out_tokens, bf16* logits_bf16, int bf16_rows, int rows, int V, int v_pad, cudaStream_t s) {
   if (rows <= 0) return 0;
-  B2_CUDA_OK(b2_launch(logits_finish_kernel, dim3(rows), dim3(256), 0, s, logits, out_tokens, logits_bf16, bf16_rows, V, v_pad));
+  B2_CUDA_OK(b2_launch(logits_finish_kernel, dim3(rows), dim3(1024), 0, s, logits, out_tokens, logits_bf16, bf16_rows, V, v_pad));
   return 0;
 }
 
