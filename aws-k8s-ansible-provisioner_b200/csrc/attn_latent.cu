@@ -276,22 +276,46 @@ __global__ void __launch_bounds__(MA_THREADS, 1) latent_attention_mma_kernel(Mma
   const int t_lo = split * per, t_hi = min(ntile, t_lo + per);
 
   // ---- stage Q (bf16), zero the padding columns of both operand slabs ----
-  for (int r = warp; r < MA_ROWS; r += MA_THREADS / 32) {
-    const int row = first + r, lane = tid & 31;
-    if (row < total) {
-      const int tok = row / g.heads, head = row - tok * g.heads;
-      const size_t base = (size_t)(q_row0 + tok) * g.heads + head;
-      const float* qa = a.q_abs + base * R;
-      const float* qr = a.q_rot + base * g.rot_dim;
-#pragma unroll 4
-      for (int d = lane; d < R; d += 32) Qs[r * DP + d] = __float2bfloat16_rn(qa[d]);
-      for (int d = lane; d < g.rot_dim; d += 32) Qs[r * DP + R + d] = __float2bfloat16_rn(qr[d]);
-      for (int d = D + lane; d < DP; d += 32) Qs[r * DP + d] = __float2bfloat16_rn(0.f);
-    } else {   // rows past the block's last: zeros, 16 bytes at a time (DP is a multiple of 8)
-      for (int c = lane; c < DP / 8; c += 32) *reinterpret_cast<uint4*>(Qs + r * DP + c * 8) = make_uint4(0, 0, 0, 0);
+  if (R % 4 == 0 && g.rot_dim % 4 == 0) {   // one flat loop over (row, four floats): many independent loads per thread
+    const int qc = R >> 2, per_row = qc + (g.rot_dim >> 2);
+#pragma unroll 8
+    for (int idx = tid; idx < MA_ROWS * per_row; idx += MA_THREADS) {
+      const int r = idx / per_row, c = idx - r * per_row, row = first + r;
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (row < total) {
+        const int tok = row / g.heads, head = row - tok * g.heads;
+        const size_t base = (size_t)(q_row0 + tok) * g.heads + head;
+        v = c < qc ? __ldg(reinterpret_cast<const float4*>(a.q_abs + base * R) + c)
+                   : __ldg(reinterpret_cast<const float4*>(a.q_rot + base * g.rot_dim) + (c - qc));
+      }
+      __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+      uint2 pk;
+      pk.x = *reinterpret_cast<unsigned*>(&lo);
+      pk.y = *reinterpret_cast<unsigned*>(&hi);
+      *reinterpret_cast<uint2*>(Qs + r * DP + c * 4) = pk;   // the rotated piece follows the latent part: column R + 4 (c - qc) = 4 c
     }
-    // key slab: only the padding columns need zeros (the copies write [0, D) of every row, zeros past the last key)
-    for (int d = D + lane; d < DP; d += 32) Ks[r * DP + d] = __float2bfloat16_rn(0.f);
+    for (int idx = tid; idx < MA_ROWS * (DP - D); idx += MA_THREADS) {
+      const int r = idx / (DP - D), d = D + idx - r * (DP - D);
+      Qs[r * DP + d] = __float2bfloat16_rn(0.f);
+      Ks[r * DP + d] = __float2bfloat16_rn(0.f);
+    }
+  } else {
+    for (int r = warp; r < MA_ROWS; r += MA_THREADS / 32) {
+      const int row = first + r, lane = tid & 31;
+      if (row < total) {
+        const int tok = row / g.heads, head = row - tok * g.heads;
+        const size_t base = (size_t)(q_row0 + tok) * g.heads + head;
+        const float* qa = a.q_abs + base * R;
+        const float* qr = a.q_rot + base * g.rot_dim;
+        for (int d = lane; d < R; d += 32) Qs[r * DP + d] = __float2bfloat16_rn(qa[d]);
+        for (int d = lane; d < g.rot_dim; d += 32) Qs[r * DP + R + d] = __float2bfloat16_rn(qr[d]);
+        for (int d = D + lane; d < DP; d += 32) Qs[r * DP + d] = __float2bfloat16_rn(0.f);
+      } else {
+        for (int d = lane; d < DP; d += 32) Qs[r * DP + d] = __float2bfloat16_rn(0.f);
+      }
+      // key slab: only the padding columns need zeros (the copies write [0, D) of every row, zeros past the last key)
+      for (int d = D + lane; d < DP; d += 32) Ks[r * DP + d] = __float2bfloat16_rn(0.f);
+    }
   }
   if (tid < MA_ROWS) {
     const int row = first + tid;
@@ -348,41 +372,66 @@ __global__ void __launch_bounds__(MA_THREADS, 1) latent_attention_mma_kernel(Mma
     wmma::store_matrix_sync(Ss + rm * 68 + kn + 16, acc[1], 68, wmma::mem_row_major);
     __syncthreads();
   };
-  // ---- sweep 1: row maxima ----
+  // ---- which row of its 16 x 16 tile each accumulator element of this thread belongs to: read back from a tile that holds
+  //      its own row numbers (the layout of a fragment is the compiler's business) ----
+  using OFrag = wmma::fragment<wmma::accumulator, 16, 16, 16, float>;
+  constexpr int NE = OFrag::num_elements;
+  OFrag oacc[4][NF];   // warp w: every row, columns [w * NF * 16, (w + 1) * NF * 16)
+  int frag_row[NE];
+  {
+    __syncthreads();
+    Ss[tid] = (float)(tid >> 4);   // 256 threads: a 16 x 16 tile, row-major
+    __syncthreads();
+    wmma::load_matrix_sync(oacc[0][0], Ss, 16, wmma::mem_row_major);
+#pragma unroll
+    for (int e = 0; e < NE; ++e) frag_row[e] = (int)oacc[0][0].x[e];
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < NF; ++j) wmma::fill_fragment(oacc[i][j], 0.f);
+  // ---- one sweep over the keys.  Weights are exp(s - ref) against a per-row reference that follows the running maximum
+  //      lazily: it moves (and the row's sums are rescaled) only when a tile's maximum exceeds it by more than REF_SLACK, so
+  //      most tiles leave the accumulators alone.  Sum, accumulator and reference stay consistent, which is all the final
+  //      division needs; weights stay below e^REF_SLACK, well inside bf16's range ----
+  constexpr float REF_SLACK = 8.0f;
   const int r4 = tid >> 2, q4 = tid & 3;  // four threads per row, 16 keys each
-  float mymax = -INFINITY;
+  float m_ref = -INFINITY, mysum = 0.f;
+  const int col0 = warp * NF * 16;
+  float* row_f = row_m;   // per-row rescale factor of the current tile (row_m itself is written after the sweep)
   for (int t = t_lo; t < t_hi; ++t) {
     const int k0 = t * MA_KEYS;
     load_keys(k0);
     scores();
     const int lim = row_pos[r4] - k0;  // keys j <= lim are visible
+    float tmax = -INFINITY;
     for (int j = q4 * 16; j < q4 * 16 + 16; ++j)
-      if (j <= lim) mymax = fmaxf(mymax, Ss[r4 * 68 + j] * g.scale);
-  }
-  mymax = fmaxf(mymax, __shfl_xor_sync(0xffffffffu, mymax, 1));
-  mymax = fmaxf(mymax, __shfl_xor_sync(0xffffffffu, mymax, 2));
-  if (q4 == 0) row_m[r4] = mymax;
-  // ---- sweep 2: P = exp(s - max), O += P . C ----
-  wmma::fragment<wmma::accumulator, 16, 16, 16, float> oacc[4][NF];   // warp w: every row, columns [w * NF * 16, (w + 1) * NF * 16)
-#pragma unroll
-  for (int i = 0; i < 4; ++i)
-#pragma unroll
-    for (int j = 0; j < NF; ++j) wmma::fill_fragment(oacc[i][j], 0.f);
-  float mysum = 0.f;
-  const int col0 = warp * NF * 16;
-  const bool one_tile = t_hi - t_lo == 1;   // a decode split: the tile of the first sweep and its scores are still staged
-  if (one_tile) __syncthreads();            // publishes row_m
-  for (int t = t_lo; t < t_hi; ++t) {
-    const int k0 = t * MA_KEYS;
-    if (!one_tile) {
-      load_keys(k0);   // its first barrier also publishes row_m
-      scores();
+      if (j <= lim) tmax = fmaxf(tmax, Ss[r4 * 68 + j] * g.scale);
+    tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 1));
+    tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 2));
+    const bool move = tmax > m_ref + REF_SLACK || (m_ref == -INFINITY && tmax > -INFINITY);
+    float f = 1.f;
+    if (move) {
+      f = m_ref == -INFINITY ? 0.f : expf(m_ref - tmax);
+      mysum *= f;
+      m_ref = tmax;
     }
-    const int lim = row_pos[r4] - k0;
-    const float m = row_m[r4];
+    if (q4 == 0) row_f[r4] = f;
+    if (__syncthreads_or(move ? 1 : 0) && t != t_lo) {   // (before the first tile the accumulators are zero)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        float fr[NE];
+#pragma unroll
+        for (int e = 0; e < NE; ++e) fr[e] = row_f[16 * i + frag_row[e]];
+#pragma unroll
+        for (int j = 0; j < NF; ++j)
+#pragma unroll
+          for (int e = 0; e < NE; ++e) oacc[i][j].x[e] *= fr[e];
+      }
+    }
     for (int j = q4 * 16; j < q4 * 16 + 16; ++j) {
       float p = 0.f;
-      if (j <= lim) p = expf(Ss[r4 * 68 + j] * g.scale - m);
+      if (j <= lim) p = expf(Ss[r4 * 68 + j] * g.scale - m_ref);
       const bf16 pb = __float2bfloat16_rn(p);
       Ps[r4 * 72 + j] = pb;
       mysum += __bfloat162float(pb);   // the weights that are summed are the weights that multiply the latents
@@ -405,7 +454,10 @@ __global__ void __launch_bounds__(MA_THREADS, 1) latent_attention_mma_kernel(Mma
   mysum += __shfl_xor_sync(0xffffffffu, mysum, 1);
   mysum += __shfl_xor_sync(0xffffffffu, mysum, 2);
   __syncthreads();  // every warp is done with Qs / Ks: they become the output tile
-  if (q4 == 0) row_l[r4] = mysum;
+  if (q4 == 0) {
+    row_l[r4] = mysum;
+    row_m[r4] = m_ref;
+  }
   const int OLD = R16 + 4;
 #pragma unroll
   for (int j = 0; j < NF; ++j) {

@@ -18,9 +18,9 @@ namespace b2 {
 
 namespace {
 
-constexpr int RT_WARPS = 4;
+constexpr int RT_WARPS = 16;
 
-// one CTA per token: the row is staged once as fp32, warp w takes experts w, w + 4, ...; thread 0 then selects
+// one CTA per token: the row is staged once as fp32, warp w takes experts w, w + 16, ...; thread 0 then selects
 template <typename TX>
 __global__ void __launch_bounds__(RT_WARPS * 32) route_kernel(const TX* __restrict__ x, const float* __restrict__ router,
                                                               const float* __restrict__ correction, RouteGeom g, int32_t* __restrict__ idx,
@@ -42,7 +42,7 @@ __global__ void __launch_bounds__(RT_WARPS * 32) route_kernel(const TX* __restri
     const float* rr = router + (size_t)e * W;
     float acc = 0.f;
     if (vec) {
-#pragma unroll 4
+#pragma unroll 8
       for (int i = lane * 4; i < W; i += 128) {
         const float4 r4 = *reinterpret_cast<const float4*>(rr + i);
         const float4 x4 = *reinterpret_cast<const float4*>(xs + i);
@@ -171,13 +171,38 @@ __global__ void __launch_bounds__(1024) route_permute_small_kernel(const int32_t
   }
 }
 
-__global__ void __launch_bounds__(128) route_combine_kernel(float* __restrict__ h, const float* __restrict__ mix, const float* __restrict__ y,
+constexpr int COMBINE_MAX_TOP = 16;   // choices staged in shared memory; wider routers read them from global memory
+__global__ void __launch_bounds__(256) route_combine_kernel(float* __restrict__ h, const float* __restrict__ mix, const float* __restrict__ y,
                                                             const float* __restrict__ weight, const int32_t* __restrict__ pair_slot, int W,
                                                             int top) {
+  __shared__ float w_s[COMBINE_MAX_TOP];
+  __shared__ int slot_s[COMBINE_MAX_TOP];
   pdl_wait();
   pdl_launch_dependents();
   const int t = blockIdx.x;
-  for (int i = threadIdx.x; i < W; i += 128) {
+  const bool staged = top <= COMBINE_MAX_TOP;
+  if (staged && (int)threadIdx.x < top) {
+    w_s[threadIdx.x] = weight[(size_t)t * top + threadIdx.x];
+    slot_s[threadIdx.x] = pair_slot[(size_t)t * top + threadIdx.x];
+  }
+  __syncthreads();
+  if (staged && W % 4 == 0) {   // (rows of h, mix and y start on 16-byte boundaries: W * 4 bytes apart from aligned bases)
+    float4* hr = reinterpret_cast<float4*>(h + (size_t)t * W);
+    const float4* mr = mix != nullptr ? reinterpret_cast<const float4*>(mix + (size_t)t * W) : nullptr;
+    for (int i = threadIdx.x; i < W / 4; i += 256) {
+      float4 acc = mr != nullptr ? mr[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int k = 0; k < top; ++k) {   // choice order
+        const float4 v = reinterpret_cast<const float4*>(y + (size_t)slot_s[k] * W)[i];
+        const float w = w_s[k];
+        acc.x = fmaf(w, v.x, acc.x); acc.y = fmaf(w, v.y, acc.y); acc.z = fmaf(w, v.z, acc.z); acc.w = fmaf(w, v.w, acc.w);
+      }
+      float4 o = hr[i];
+      o.x += acc.x; o.y += acc.y; o.z += acc.z; o.w += acc.w;
+      hr[i] = o;
+    }
+    return;
+  }
+  for (int i = threadIdx.x; i < W; i += 256) {
     float acc = mix != nullptr ? mix[(size_t)t * W + i] : 0.f;
     for (int k = 0; k < top; ++k) acc = fmaf(weight[(size_t)t * top + k], y[(size_t)pair_slot[(size_t)t * top + k] * W + i], acc);
     h[(size_t)t * W + i] += acc;
@@ -225,7 +250,7 @@ int launch_route_permute(const int32_t* idx, int T, int top, int experts, int32_
 int launch_route_combine(float* h, const float* mix, const float* y, const float* weight, const int32_t* pair_slot, int T, int W, int top,
                          cudaStream_t s) {
   if (T <= 0) return 0;
-  B2_CUDA_OK(b2_launch(route_combine_kernel, dim3(T), dim3(128), 0, s, h, mix, y, weight, pair_slot, W, top));
+  B2_CUDA_OK(b2_launch(route_combine_kernel, dim3(T), dim3(256), 0, s, h, mix, y, weight, pair_slot, W, top));
   return 0;
 }
 

@@ -150,6 +150,29 @@ def test_bf16_prompt_sized_and_decode_sized_kernels_agree():
         assert rows_over(np.stack(dec), ref[300:], BF16_BAR) <= 1 and rows_over(np.stack(dec), lw[300:], BF16_BAR) <= 1
 
 
+@pytest.mark.parametrize("nseq", [3, 12, 27, 50])
+def test_bf16_decode_batches_of_many_sizes(nseq):
+    """bf16 decode steps whose batch fills one, two, four and eight 8-row token tiles of the weight-streaming products (and
+    leaves the last tile ragged), sequences of unequal length: every sequence's logits against the oracle's for that sequence
+    alone, and against the same sequence decoded in a batch of one."""
+    cfg = cfg_c()
+    w = random_weights(cfg, seed=31)
+    prompts = [tokens(cfg, 3 + (7 * i) % 41, 100 + i) for i in range(nseq)]
+    refs = [Oracle(cfg, w).forward(p).numpy()[-1] for p in prompts]   # (an oracle holds one sequence)
+    with engine(cfg, w, f32=False, max_seqs=nseq, num_blocks=4 * nseq + 8, max_model_len=64, max_batch_tokens=2048) as e:
+        sids = [e.seq_create(64) for _ in prompts]
+        e.prefill_logits(sids, [p[:-1] for p in prompts], [])
+        e.decode_step(sids, in_tokens=[p[-1] for p in prompts], want_output=False)
+        lg = e.get_logits(nseq)
+        assert rows_over(lg, np.stack(refs), BF16_BAR) <= max(1, nseq // 25)
+    with engine(cfg, w, f32=False, max_seqs=1, num_blocks=12, max_model_len=64, max_batch_tokens=64) as e:
+        k = nseq - 1
+        alone = e.seq_create(64)
+        e.prefill_logits([alone], [prompts[k][:-1]], [])
+        e.decode_step([alone], in_tokens=[prompts[k][-1]], want_output=False)
+        assert rows_over(e.get_logits(1), lg[k:k + 1], BF16_BAR) == 0
+
+
 def test_prefill_against_token_by_token_decoding():
     cfg = cfg_a()
     w = sharpen(random_weights(cfg, seed=5), cfg)
