@@ -288,6 +288,9 @@ struct b2_engine {
           *l_tile_row0 = nullptr, *l_ntiles = nullptr;
   int l_max_top = 0, l_tiles_cap = 0, l_rows_cap = 0, l_offsets_stride = 0;
   float* l_attn_scratch = nullptr;   // key splits of a decode step's latent attention
+  bf16* l_xperm = nullptr;           // prompt-sized steps: the feed-forward input rows in expert (slot) order
+  float* l_upf = nullptr;            // ... and the experts' up-projection sums before the activation
+  int32_t* h_offsets = nullptr;      // pinned: the experts' slot ranges of the step, read back for the per-expert launches
   size_t l_attn_scratch_floats = 0;
   float* dbg_hidden_f32 = nullptr;
 };
@@ -839,6 +842,8 @@ int forward_layers(b2_engine* e, const Lane& ln, int T, int ntiles) {
 // layer share one statistic (one kernel).  Mixer = latent attention in absorbed form (attn_latent.cu); feed-forward =
 // routed squared-ReLU experts as ragged groups of gemm_any.cu.  `rows` (device, nlast entries; null = every row) selects
 // the positions that get logits.  Operands are bf16, or fp32 when the engine was created with compute_f32.
+constexpr int LIST_TC_EXPERT_ROWS = 2048;   // (token, choice) pairs of a step from which the experts' products go expert by expert to the tcgen05 kernel
+
 int forward_list(b2_engine* e, int T, int ntiles, int nlast) {
   const b2_config& c = e->cfg;
   const int W = c.hidden, f = e->f32 ? 1 : 0;
@@ -931,24 +936,59 @@ int forward_list(b2_engine* e, int T, int ntiles, int nlast) {
         KL k(e, B2K_MISC);
         if (!k.skip()) B2_TRY(launch_route_permute(e->l_idx, T, sp.top, sp.experts, e->l_offsets, e->l_offsets_stride, e->l_slot_token, e->l_pair_slot, st));
       }
-      const int max_tiles = std::min(e->l_tiles_cap, (T * sp.top + any_gemm_tile_rows() - 1) / any_gemm_tile_rows() + sp.experts);
-      if (T * sp.top > any_gemm_ragged_rows_limit() || W > 16384 || sp.ff_dim > 16384) {   // (a decode-sized step streams the experts' weights group by group instead)
-        KL k(e, B2K_MISC);
-        if (!k.skip()) B2_TRY(launch_ragged_tiles(e->l_offsets, sp.experts, e->l_tile_group, e->l_tile_row0, e->l_ntiles, max_tiles, st));
-      }
-      AnyGemm a;
-      a.tile_group = e->l_tile_group; a.tile_row0 = e->l_tile_row0; a.n_tiles = e->l_ntiles; a.group_offsets = e->l_offsets;
-      {
-        KL k(e, B2K_GEMM_GATEUP);  // act[slot] = relu(U_e x[token(slot)])^2
-        a.A = e->l_x2; a.a_rows = e->l_slot_token; a.W = L.up; a.C = e->l_act; a.N = sp.ff_dim; a.K = W; a.lda = W; a.ldw = W; a.ldc = sp.ff_dim;
-        a.w_bs = (long)sp.ff_dim * W; a.epilogue = ANY_EPI_RELU2;
-        if (!k.skip()) B2_TRY(launch_gemm_any(a, f, f, f, 1, max_tiles, st, T * sp.top, sp.experts));
-      }
-      {
-        KL k(e, B2K_GEMM_DOWN);  // y[slot] = D_e act[slot]
-        a.A = e->l_act; a.a_rows = nullptr; a.W = L.down; a.C = e->l_y; a.N = W; a.K = sp.ff_dim; a.lda = sp.ff_dim; a.ldw = sp.ff_dim; a.ldc = W;
-        a.w_bs = (long)W * sp.ff_dim; a.epilogue = ANY_EPI_STORE;
-        if (!k.skip()) B2_TRY(launch_gemm_any(a, f, f, 1, 1, max_tiles, st, T * sp.top, sp.experts));
+      // Prompt-sized bf16 steps: the rows are gathered into expert order, the experts' slot ranges are read back (one small
+      // copy and a stream synchronisation per layer: nothing beside a pass that takes milliseconds), and every expert's two
+      // products are plain dense projections on the tcgen05 kernel; the activation rounds the fp32 sums to the bf16 operand
+      // of the second product.  Everything else (decode steps, short portions, fp32, odd sizes) runs as ragged groups.
+      const bool tc_experts = use_tc && !f && ntiles > 0 && e->l_xperm != nullptr && T * sp.top >= LIST_TC_EXPERT_ROWS && W % 64 == 0 &&
+                              sp.ff_dim % 64 == 0 && W >= 128 && sp.ff_dim >= 128 && e->skip_mask == 0;
+      if (tc_experts) {
+        B2_CUDA_OK(cudaMemcpyAsync(e->h_offsets, e->l_offsets, (size_t)(sp.experts + 1) * 4, cudaMemcpyDeviceToHost, st));
+        {
+          KL k(e, B2K_MISC);
+          B2_TRY(launch_gather_rows((const bf16*)e->l_x2, e->l_slot_token, e->l_xperm, T * sp.top, W, st));
+        }
+        B2_CUDA_OK(cudaStreamSynchronize(st));
+        const int32_t* off = e->h_offsets;
+        B2_REQUIRE(off[0] == 0 && off[sp.experts] == T * sp.top, "layer %d: the experts' slot ranges do not cover the step's %d pairs", l, T * sp.top);
+        {
+          KL k(e, B2K_GEMM_GATEUP);
+          for (int x = 0; x < sp.experts; ++x)
+            if (off[x + 1] > off[x])
+              B2_TRY(dense(e->l_xperm + (size_t)off[x] * W, (const bf16*)L.up + (size_t)x * sp.ff_dim * W, e->l_upf + (size_t)off[x] * sp.ff_dim,
+                           off[x + 1] - off[x], sp.ff_dim, W, 1.f));
+        }
+        {
+          KL k(e, B2K_ACT);
+          B2_TRY(launch_relu2_round(e->l_upf, (bf16*)e->l_act, (size_t)T * sp.top * sp.ff_dim, st));
+        }
+        {
+          KL k(e, B2K_GEMM_DOWN);
+          for (int x = 0; x < sp.experts; ++x)
+            if (off[x + 1] > off[x])
+              B2_TRY(dense((const bf16*)e->l_act + (size_t)off[x] * sp.ff_dim, (const bf16*)L.down + (size_t)x * W * sp.ff_dim,
+                           e->l_y + (size_t)off[x] * W, off[x + 1] - off[x], W, sp.ff_dim, 1.f));
+        }
+      } else {
+        const int max_tiles = std::min(e->l_tiles_cap, (T * sp.top + any_gemm_tile_rows() - 1) / any_gemm_tile_rows() + sp.experts);
+        if (T * sp.top > any_gemm_ragged_rows_limit() || W > 16384 || sp.ff_dim > 16384) {   // (a decode-sized step streams the experts' weights group by group instead)
+          KL k(e, B2K_MISC);
+          if (!k.skip()) B2_TRY(launch_ragged_tiles(e->l_offsets, sp.experts, e->l_tile_group, e->l_tile_row0, e->l_ntiles, max_tiles, st));
+        }
+        AnyGemm a;
+        a.tile_group = e->l_tile_group; a.tile_row0 = e->l_tile_row0; a.n_tiles = e->l_ntiles; a.group_offsets = e->l_offsets;
+        {
+          KL k(e, B2K_GEMM_GATEUP);  // act[slot] = relu(U_e x[token(slot)])^2
+          a.A = e->l_x2; a.a_rows = e->l_slot_token; a.W = L.up; a.C = e->l_act; a.N = sp.ff_dim; a.K = W; a.lda = W; a.ldw = W; a.ldc = sp.ff_dim;
+          a.w_bs = (long)sp.ff_dim * W; a.epilogue = ANY_EPI_RELU2;
+          if (!k.skip()) B2_TRY(launch_gemm_any(a, f, f, f, 1, max_tiles, st, T * sp.top, sp.experts));
+        }
+        {
+          KL k(e, B2K_GEMM_DOWN);  // y[slot] = D_e act[slot]
+          a.A = e->l_act; a.a_rows = nullptr; a.W = L.down; a.C = e->l_y; a.N = W; a.K = sp.ff_dim; a.lda = sp.ff_dim; a.ldw = sp.ff_dim; a.ldc = W;
+          a.w_bs = (long)W * sp.ff_dim; a.epilogue = ANY_EPI_STORE;
+          if (!k.skip()) B2_TRY(launch_gemm_any(a, f, f, 1, 1, max_tiles, st, T * sp.top, sp.experts));
+        }
       }
     }
     {
@@ -1534,6 +1574,11 @@ int list_engine_alloc(b2_engine* e) {
     }
     e->l_attn_scratch_floats = latent_attention_scratch_floats(bucket_batch(c.max_seqs), max_heads, max_rank);
     B2_TRY(dalloc(&e->l_attn_scratch, e->l_attn_scratch_floats));
+    if (max_top > 0 && Tc * max_top >= (size_t)LIST_TC_EXPERT_ROWS) {   // prompt-sized expert products on the tcgen05 projection kernel
+      B2_TRY(dalloc(&e->l_xperm, Tc * max_top * W));
+      B2_TRY(dalloc(&e->l_upf, Tc * max_top * max_ff));
+      B2_CUDA_OK(cudaMallocHost(&e->h_offsets, (size_t)(max_exp + 1) * sizeof(int32_t)));
+    }
   }
   B2_CUDA_OK(cudaMemset(e->l_ntiles, 0, 4));
   B2_CUDA_OK(cudaMemset(e->l_pair_slot, 0, Tc * max_top * 4));
@@ -2187,6 +2232,7 @@ extern "C" void b2_engine_free(b2_engine* e) {
   if (e->ev_tok) cudaEventDestroy(e->ev_tok);
   F(e->partial2); F(e->attn_scratch2); F(e->ssq);
   F(e->l_embed); F(e->l_head); F(e->l_embed_gain); F(e->l_final_gain); F(e->l_pool); F(e->l_h); F(e->l_qd); F(e->l_qrot); F(e->l_qabs);
+  F(e->l_xperm); F(e->l_upf); if (e->h_offsets) cudaFreeHost(e->h_offsets);
   F(e->l_mix); F(e->l_y); F(e->l_rw); F(e->l_logits); F(e->l_x1); F(e->l_x2); F(e->l_qnope); F(e->l_olat); F(e->l_av); F(e->l_act); F(e->l_xl);
   F(e->l_attn_scratch); F(e->l_idx); F(e->l_offsets); F(e->l_slot_token); F(e->l_pair_slot); F(e->l_tile_group); F(e->l_tile_row0); F(e->l_ntiles); F(e->dbg_hidden_f32);
   for (auto& L : e->ll) {

@@ -2,7 +2,7 @@
 // by plain fused multiply-adds: no reduced-precision matrix mode), as one strided batch or as ragged groups.
 //
 // The tcgen05 projections (gemm_tc.cu and friends) are built for bf16 operands whose sizes are multiples of their tiles.
-// Models with a layer list bring shapes that are not (a latent of 96, 12 experts of 80 rows, a vocabulary of 500), a
+// Models with a layer list bring shapes that are not (a latent of 96, 10 experts of 80 rows, a vocabulary of 500), a
 // true-fp32 mode, per-head products against a slice of a wider activation row, and experts that each see their own
 // subset of the tokens.  This kernel takes all of them:
 //   * strided batch: blockIdx.z picks (A + z * a_bs, W + z * w_bs, C + z * c_bs): one launch for all heads of an

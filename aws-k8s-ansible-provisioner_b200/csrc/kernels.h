@@ -286,6 +286,8 @@ int launch_route(const void* x, int x_f32, const float* router, const float* cor
 // offsets + 2 * stride; zero it once when it is allocated), slot_token [T*top] (slot -> token), pair_slot [T*top] (pair -> slot).
 int launch_route_permute(const int32_t* idx, int T, int top, int experts, int32_t* offsets, int stride, int32_t* slot_token,
                          int32_t* pair_slot, cudaStream_t s);
+// act[i] = bf16(max(up[i], 0)^2), n a multiple of 4
+int launch_relu2_round(const float* up, bf16* act, size_t n, cudaStream_t s);
 // h[t] += sum_k weight[t][k] * y[pair_slot[t*top + k]]   (+ mix[t] when given); fp32
 int launch_route_combine(float* h, const float* mix, const float* y, const float* weight, const int32_t* pair_slot, int T, int W, int top,
                          cudaStream_t s);

@@ -25,15 +25,15 @@ template <typename TX>
 __global__ void __launch_bounds__(RT_WARPS * 32) route_kernel(const TX* __restrict__ x, const float* __restrict__ router,
                                                               const float* __restrict__ correction, RouteGeom g, int32_t* __restrict__ idx,
                                                               float* __restrict__ weight, int T, int W) {
-  extern __shared__ float sm[];  // s [E], choice [E], x row [W]
+  extern __shared__ __align__(16) float sm[];  // x row [W rounded up to 4] (read as float4), s [E], choice [E]
   pdl_wait();
   pdl_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x;
   const int E = g.experts;
-  float* s = sm;
+  float* xs = sm;
+  float* s = xs + ((W + 3) & ~3);
   float* ch = s + E;
-  float* xs = ch + E;
   const TX* xr = x + (size_t)t * W;
   for (int i = threadIdx.x; i < W; i += RT_WARPS * 32) xs[i] = (float)xr[i];
   __syncthreads();
@@ -209,7 +209,31 @@ __global__ void __launch_bounds__(256) route_combine_kernel(float* __restrict__ 
   }
 }
 
+// act = bf16(max(up, 0)^2): the experts' activation between the two dense products of a prompt-sized step
+__global__ void __launch_bounds__(256) relu2_round_kernel(const float4* __restrict__ up, uint2* __restrict__ act, size_t n4) {
+  pdl_wait();
+  pdl_launch_dependents();
+  for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < n4; i += (size_t)gridDim.x * 256) {
+    const float4 v = up[i];
+    const float a = fmaxf(v.x, 0.f), b = fmaxf(v.y, 0.f), c = fmaxf(v.z, 0.f), d = fmaxf(v.w, 0.f);
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(a * a, b * b), hi = __floats2bfloat162_rn(c * c, d * d);
+    uint2 o;
+    o.x = *reinterpret_cast<const uint32_t*>(&lo);
+    o.y = *reinterpret_cast<const uint32_t*>(&hi);
+    act[i] = o;
+  }
+}
+
 }  // namespace
+
+int launch_relu2_round(const float* up, bf16* act, size_t n, cudaStream_t s) {
+  if (n == 0) return 0;
+  if (n % 4 != 0) return -22;   // (rows are multiples of 64 wide on this path)
+  const size_t n4 = n / 4;
+  const int grid = (int)std::min<size_t>((n4 + 255) / 256, 148 * 16);
+  B2_CUDA_OK(b2_launch(relu2_round_kernel, dim3(grid), dim3(256), 0, s, (const float4*)up, (uint2*)act, n4));
+  return 0;
+}
 
 int launch_route(const void* x, int x_f32, const float* router, const float* correction, const RouteGeom& g, int32_t* idx, float* weight,
                  int T, int W, cudaStream_t s) {
@@ -218,7 +242,7 @@ int launch_route(const void* x, int x_f32, const float* router, const float* cor
   B2_REQUIRE(g.keep >= 1 && g.keep <= g.groups, "route: keep %d outside [1, %d]", g.keep, g.groups);
   B2_REQUIRE(g.top >= 1 && g.top <= g.keep * (g.experts / g.groups), "route: top %d exceeds the %d experts of the kept groups", g.top,
              g.keep * (g.experts / g.groups));
-  const size_t smem = ((size_t)2 * g.experts + W) * sizeof(float);
+  const size_t smem = ((size_t)2 * g.experts + ((W + 3) & ~3)) * sizeof(float);
   B2_REQUIRE(smem <= 48 * 1024, "route: %d experts and width %d need %zu bytes of shared memory", g.experts, W, smem);
   const dim3 grid(T);
   if (x_f32)

@@ -185,7 +185,7 @@ def hf_cpu_decode(batch: int, ctx: int, steps: int, warmup: int, budget_s: float
     `budget_s`, the per-step sample is cut to a sub-batch and said so."""
     import torch
     from transformers import DynamicCache
-    from oracle.qwen3_oracle import QWEN3_0_6B, hf_model  # the checker's model builder (CPU arm only)
+    from oracle.qwen3_oracle import QWEN3_0_6B, hf_model  # the oracle's model builder (CPU arm only)
 
     arch = QWEN3_0_6B
     # all the host threads the CPU arm can use: torchrun exports OMP_NUM_THREADS=1 to every rank, which

@@ -275,7 +275,7 @@ int b2k_qkv_rope(const void* x_bf16, const void* w_qkv_bf16, const void* qnorm_w
                  const int32_t* positions, const int32_t* slots, void* q_out, void* k_pages, void* v_pages, int T, int nq,
                  int nkv, int K, int block_size, float eps, void* stream);
 
-/* The decode step's norm-free layer chain (round 2): the two projections that feed the residual stream update it
+/* The decode step's norm-free layer chain: the two projections that feed the residual stream update it
  * themselves, and the two projections that read it normalise it as they load it, so that no RMSNorm kernel runs between
  * them (HF:models/qwen3/modeling_qwen3.py:339-351 for the adds, :50-62 for the norm).
  * b2k_linear_resid: h[T][N] (bf16, in place) = bf16(h + bf16(x[T][K] . W[N][K]^T)), T <= 64, N % 128 == 0, K % 512 == 0,

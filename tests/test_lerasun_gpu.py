@@ -150,6 +150,31 @@ def test_bf16_prompt_sized_and_decode_sized_kernels_agree():
         assert rows_over(np.stack(dec), ref[300:], BF16_BAR) <= 1 and rows_over(np.stack(dec), lw[300:], BF16_BAR) <= 1
 
 
+def test_bf16_expert_products_of_a_long_step():
+    """bf16: a step with more than 2048 (token, choice) pairs runs every expert's two products as dense tcgen05 projections over
+    rows gathered into expert order; shorter steps run them as ragged groups.  Two unequal prompts in one long step against the
+    oracle and against the same prompts fed in short portions.  One expert's correction keeps it from ever being chosen, so an
+    empty slot range is among the experts."""
+    m = mixer(2, 32, 16, 32, 64, 0.2)
+    cfg = {"architecture": "Lerasun", "vocab": 211, "width": 128, "logit_scale": 0.5, "norm": {"eps": 1e-6}, "layers": [
+        layer(m, moe(128, 5, 2, 1, 1)), layer(dict(m, kv_from=0), moe(192, 6, 3, 3, 2))]}
+    w = random_weights(cfg, seed=41)
+    w["l0.mlp.correction"][3] = -50.0
+    prompts = [tokens(cfg, 640, 42), tokens(cfg, 470, 43)]
+    refs = [Oracle(cfg, w).forward(p).numpy() for p in prompts]
+    with engine(cfg, w, f32=False, max_batch_tokens=1280, num_blocks=200) as e:
+        sids = [e.seq_create(700), e.seq_create(700)]
+        rows = list(range(600, 640)) + list(range(640 + 430, 640 + 470))
+        long_step, _ = e.prefill_logits(sids, prompts, rows)
+        ref = np.concatenate([refs[0][600:], refs[1][430:]])
+        assert rows_over(long_step, ref, BF16_BAR) <= 1
+        t = [e.seq_create(700), e.seq_create(700)]
+        for lo in range(0, 400, 200):
+            e.prefill_logits(t, [p[lo:lo + 200] for p in prompts], [])
+        short = [e.prefill_logits([t[i]], [prompts[i][400:]], list(range(len(prompts[i]) - 440, len(prompts[i]) - 400)))[0] for i in range(2)]
+        assert rows_over(np.concatenate(short), long_step, BF16_BAR) <= 1
+
+
 @pytest.mark.parametrize("nseq", [3, 12, 27, 50])
 def test_bf16_decode_batches_of_many_sizes(nseq):
     """bf16 decode steps whose batch fills one, two, four and eight 8-row token tiles of the weight-streaming products (and
