@@ -175,6 +175,24 @@ def test_bf16_expert_products_of_a_long_step():
         assert rows_over(np.concatenate(short), long_step, BF16_BAR) <= 1
 
 
+@pytest.mark.parametrize("experts,groups,keep,top", [(1, 1, 1, 1), (3, 1, 1, 2), (5, 5, 3, 2), (7, 1, 1, 7), (9, 3, 2, 4), (15, 5, 2, 1), (34, 2, 1, 17)])
+def test_router_of_any_expert_count(experts, groups, keep, top):
+    """Expert counts that are odd, prime, one, or more than a warp's lanes, with a width the router reads four numbers at a time:
+    fp32 engine against the oracle on a prompt and a few decoded tokens (a wrong choice or weight moves the logits far above fp32 rounding)."""
+    cfg = {"architecture": "Lerasun", "vocab": 61, "width": 72, "logit_scale": 1.0, "norm": {"eps": 1e-6}, "layers": [
+        layer(mixer(2, 8, 4, 8, 16, 0.3), moe(12, experts, top, groups, keep)), layer(mixer(2, 8, 4, 8, 16, 0.3, kv_from=0), moe(20, experts, top, groups, keep))]}
+    w = random_weights(cfg, seed=50 + experts)
+    toks = tokens(cfg, 45, 51)
+    ref = Oracle(cfg, w).forward(toks).numpy()
+    with engine(cfg, w) as e:
+        sid = e.seq_create(64)
+        lg, _ = e.prefill_logits([sid], [toks[:40]], list(range(40)))
+        assert err(lg, ref[:40]) < F32_BAR
+        for p in range(40, 45):
+            e.decode_step([sid], in_tokens=[toks[p]], want_output=False)
+            assert err(e.get_logits(1)[0], ref[p]) < F32_BAR
+
+
 @pytest.mark.parametrize("nseq", [3, 12, 27, 50])
 def test_bf16_decode_batches_of_many_sizes(nseq):
     """bf16 decode steps whose batch fills one, two, four and eight 8-row token tiles of the weight-streaming products (and
