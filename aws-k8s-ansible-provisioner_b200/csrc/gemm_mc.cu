@@ -4,7 +4,7 @@
 // Why: the persistent 128 x 256 tile kernel of gemm_tc.cu moves 48 KB from L2 into shared memory per 64-wide k-block
 // (16 KB of weights + 32 KB of tokens) for 532 cycles of tcgen05.mma: 90 bytes per cycle and SM, more than an SM gets
 // from L2 when all 148 ask at once -- ncu shows the tensor pipe 52-68 % active and the share rising with K, i.e. with the
-// weight of the main loop (profiles/r02_prefill_full_raw.csv).  Here two CTAs take two ADJACENT weight-row tiles of the same
+// weight of the main loop (profiles/qwen3_b_prefill_full_raw.csv).  Here two CTAs take two ADJACENT weight-row tiles of the same
 // 256-token tile: each loads its own 16 KB of weights and only HALF of the token rows (16 KB), and the TMA engine writes that
 // half into BOTH CTAs' shared memory (cp.async.bulk.tensor ... .multicast::cluster; the tensor maps cover this GPU's memory
 // only).  32 KB per k-block and SM instead of 48.

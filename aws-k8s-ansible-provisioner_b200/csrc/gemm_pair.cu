@@ -4,7 +4,7 @@
 // for at most 64 tokens.  Same tcgen05 / TMEM / TMA machinery and the same swap-AB layout as gemm_tc.cu (weight rows on
 // MMA-M, tokens on MMA-N); what is new is how split-K is reduced.
 //
-// Why: in the captured step (tools/step_timeline.py, profiles/r02_step_timeline_one_lane.txt) a projection cost
+// Why: in the captured step (tools/step_timeline.py, profiles/qwen3_b_step_timeline_one_lane.txt) a projection cost
 // ~1.4 us of hand-off + ~3.5 us of work and the element-wise kernel behind it another ~1.3 + ~2.3 us, most of which
 // is writing fp32 split-K partials to L2, a kernel boundary, and reading them back.  The projections need split-K
 // because one SM streams weights at ~60 GB/s at best: the 8-13 MB of a projection have to be spread over ~100 SMs.

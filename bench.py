@@ -382,7 +382,7 @@ def run_b200(args, rank, world, local, dist):
     # own traffic/algorithmic ratio, which is what the figure is for)
     traffic = None
     try:
-        with open(os.path.join(ROOT, "profiles", "r02_attn_traffic.json")) as f:
+        with open(os.path.join(ROOT, "profiles", "qwen3_b_attn_traffic.json")) as f:
             tj = json.load(f)
         traffic = step_pass_bytes * (tj["dram_bytes_read"] + tj["dram_bytes_write"]) / tj["algorithmic_bytes"]
     except (OSError, KeyError, ValueError):
@@ -405,7 +405,7 @@ def run_b200(args, rank, world, local, dist):
         "repeats": REPEATS, "ms_per_step_runs": [round(m / K, 5) for m in ms_runs],
         "roofline": {"bound": "hbm", "kernel": "attn_decode_kernel (one layer's pass)", "achieved": achieved, "peak": peak,
                      "unit": "GB/s", "frac": achieved / peak, "traffic": traffic,
-                     "traffic_source": "ncu --set full capture at context 641 (profiles/r02_attn_traffic.json): DRAM read+write = 1.024 x algorithmic, applied to this context", "peak_kind": peak_kind,
+                     "traffic_source": "ncu --set full capture at context 641 (profiles/qwen3_b_attn_traffic.json): DRAM read+write = 1.024 x algorithmic, applied to this context", "peak_kind": peak_kind,
                      "how": "in-step: (step - step without the attention class) / layers",
                      "bytes_per_launch": step_pass_bytes, "ms_per_launch": attn_ms_in_step, "context": s_mean,
                      "ms_per_step_without_attention": ms_noattn / K,

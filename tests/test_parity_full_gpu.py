@@ -8,7 +8,7 @@ flip must be explained by the logit noise that was measured, nothing else.  Ever
 tokens, so the logits of ALL 128 steps are compared, also after such a flip.  The noise floor of the oracle itself is
 HF's second attention implementation (eager vs sdpa) on the same weights and tokens.
 
-The counts and gaps are written to gpurun_out/parity.json (tests/_util.record_parity), copied to profiles/r02_parity.json."""
+The counts and gaps are written to gpurun_out/parity.json (tests/_util.record_parity), copied to profiles/qwen3_b_parity.json."""
 import os
 
 import numpy as np

@@ -13,7 +13,7 @@ ncu --metrics gpu__time_duration.sum --clock-control none -s ${SKIP:-2400} -c ${
     --log-file gpurun_out/launches.csv $CMD > gpurun_out/ncu_launches.log 2>&1
 echo "launch list rc=$?"
 else
-ncu --set full --clock-control none --import-source on -k regex:${KERNEL:-attn_decode_kernel} -s ${KSKIP:-100} -c 2 \
+ncu --set full --clock-control none -k regex:${KERNEL:-attn_decode_kernel} -s ${KSKIP:-100} -c 2 \
     -f -o gpurun_out/prof_${KERNEL:-attn_decode_kernel} $CMD > gpurun_out/ncu_full.log 2>&1
 echo "full capture rc=$?"
 fi
