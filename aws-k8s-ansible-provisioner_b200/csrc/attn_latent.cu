@@ -324,6 +324,9 @@ __global__ void __launch_bounds__(MA_THREADS, 1) latent_attention_mma_kernel(Mma
     row_l[tid] = 0.f;
   }
   const int32_t* bt = a.block_table + (size_t)bt_row * a.bt_stride;
+  // 16-row groups of the tile that hold real rows: a decode step brings `heads` rows, and the groups past them are zero
+  // queries whose weights are all zero, so neither product needs to touch them
+  const int live_groups = (min(MA_ROWS, total - first) + 15) >> 4;
   const bool vec = (D % 8 == 0);
   auto load_keys = [&](int k0) {
     __syncthreads();  // the previous tile's reads of Ks / Ss / Ps are done
@@ -357,19 +360,35 @@ __global__ void __launch_bounds__(MA_THREADS, 1) latent_attention_mma_kernel(Mma
     wmma::fragment<wmma::accumulator, 16, 16, 16, float> acc[2];
     wmma::fill_fragment(acc[0], 0.f);
     wmma::fill_fragment(acc[1], 0.f);
-    const int rm = (warp >> 1) * 16, kn = (warp & 1) * 32;
-    for (int d = 0; d < D16; d += 16) {
-      wmma::fragment<wmma::matrix_a, 16, 16, 16, bf16, wmma::row_major> fq;
-      wmma::fragment<wmma::matrix_b, 16, 16, 16, bf16, wmma::col_major> fk;
-      wmma::load_matrix_sync(fq, Qs + rm * DP + d, DP);
-#pragma unroll
-      for (int j = 0; j < 2; ++j) {
-        wmma::load_matrix_sync(fk, Ks + (kn + 16 * j) * DP + d, DP);
-        wmma::mma_sync(acc[j], fq, fk, acc[j]);
+    if (live_groups == 1) {   // sixteen rows: warps 0..3 take sixteen keys each (the other row groups are never read)
+      if (warp < 4) {
+        for (int d = 0; d < D16; d += 16) {
+          wmma::fragment<wmma::matrix_a, 16, 16, 16, bf16, wmma::row_major> fq;
+          wmma::fragment<wmma::matrix_b, 16, 16, 16, bf16, wmma::col_major> fk;
+          wmma::load_matrix_sync(fq, Qs + d, DP);
+          wmma::load_matrix_sync(fk, Ks + (16 * warp) * DP + d, DP);
+          wmma::mma_sync(acc[0], fq, fk, acc[0]);
+        }
+        wmma::store_matrix_sync(Ss + 16 * warp, acc[0], 68, wmma::mem_row_major);
       }
+      __syncthreads();
+      return;
     }
-    wmma::store_matrix_sync(Ss + rm * 68 + kn, acc[0], 68, wmma::mem_row_major);
-    wmma::store_matrix_sync(Ss + rm * 68 + kn + 16, acc[1], 68, wmma::mem_row_major);
+    const int rm = (warp >> 1) * 16, kn = (warp & 1) * 32;
+    if (rm < 16 * live_groups) {
+      for (int d = 0; d < D16; d += 16) {
+        wmma::fragment<wmma::matrix_a, 16, 16, 16, bf16, wmma::row_major> fq;
+        wmma::fragment<wmma::matrix_b, 16, 16, 16, bf16, wmma::col_major> fk;
+        wmma::load_matrix_sync(fq, Qs + rm * DP + d, DP);
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          wmma::load_matrix_sync(fk, Ks + (kn + 16 * j) * DP + d, DP);
+          wmma::mma_sync(acc[j], fq, fk, acc[j]);
+        }
+      }
+      wmma::store_matrix_sync(Ss + rm * 68 + kn, acc[0], 68, wmma::mem_row_major);
+      wmma::store_matrix_sync(Ss + rm * 68 + kn + 16, acc[1], 68, wmma::mem_row_major);
+    }
     __syncthreads();
   };
   // ---- which row of its 16 x 16 tile each accumulator element of this thread belongs to: read back from a tile that holds
@@ -440,14 +459,16 @@ __global__ void __launch_bounds__(MA_THREADS, 1) latent_attention_mma_kernel(Mma
     for (int kk = 0; kk < MA_KEYS; kk += 16) {
       wmma::fragment<wmma::matrix_a, 16, 16, 16, bf16, wmma::row_major> fp[4];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) wmma::load_matrix_sync(fp[i], Ps + (16 * i) * 72 + kk, 72);
+      for (int i = 0; i < 4; ++i)
+        if (i < live_groups) wmma::load_matrix_sync(fp[i], Ps + (16 * i) * 72 + kk, 72);
 #pragma unroll
       for (int j = 0; j < NF; ++j) {
         if (col0 + 16 * j >= R16) continue;  // warp-uniform
         wmma::fragment<wmma::matrix_b, 16, 16, 16, bf16, wmma::row_major> fv;
         wmma::load_matrix_sync(fv, Ks + kk * DP + col0 + 16 * j, DP);
 #pragma unroll
-        for (int i = 0; i < 4; ++i) wmma::mma_sync(oacc[i][j], fp[i], fv, oacc[i][j]);
+        for (int i = 0; i < 4; ++i)
+          if (i < live_groups) wmma::mma_sync(oacc[i][j], fp[i], fv, oacc[i][j]);
       }
     }
   }
