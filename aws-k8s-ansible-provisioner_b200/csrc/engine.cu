@@ -86,7 +86,15 @@ struct ListLayer {
   int cache_region = -1;      // which cache region the layer attends over (its own, or layer kv_from's)
   void *wqd = nullptr, *ukT = nullptr, *uv = nullptr, *wo = nullptr, *up = nullptr, *down = nullptr;
   float *gain1 = nullptr, *gain2 = nullptr, *lat_gain = nullptr, *sink = nullptr, *router = nullptr, *corr = nullptr;
+  // Mixers with per-head keys and values (Kedasun): wqd holds q | k | v (| the head gates) as one projection of nqd rows, `up` holds
+  // gate | up of the dense feed-forward, `down` its output projection; norms before (gain1, gain2) and behind (gain1b, gain2b) each sublayer.
+  int nk = 0, nv = 0;         // kv_heads * dim, kv_heads * vdim
+  int v_region = -1;          // cache region of the values (cache_region holds the keys)
+  int vmix_mode = 0;          // 0 no value mixing, 1 the layer supplies the first values, 2 it blends with them
+  float *gain1b = nullptr, *gain2b = nullptr, *qkv_bias = nullptr, *o_bias = nullptr, *conv_w = nullptr, *talk = nullptr, *vmix = nullptr;
+  float* conv_ring = nullptr; // [sequence slots][taps][q | k | v channels], row = position mod taps: the projected rows a sequence's next convolutions need
 };
+inline bool list_arch(int arch) { return arch == B2_ARCH_LERASUN || arch == B2_ARCH_KEDASUN; }
 
 struct Seq {
   bool active = false;
@@ -287,6 +295,11 @@ struct b2_engine {
   int32_t *l_idx = nullptr, *l_offsets = nullptr, *l_slot_token = nullptr, *l_pair_slot = nullptr, *l_tile_group = nullptr,
           *l_tile_row0 = nullptr, *l_ntiles = nullptr;
   int l_max_top = 0, l_tiles_cap = 0, l_rows_cap = 0, l_offsets_stride = 0;
+  // per-head attention (Kedasun): fp32 queries, the first value-mixing layer's values of the step's tokens, the per-head sums
+  // that weight mixing combines; and, per token row of the step, its sequence slot and the row range of its portion
+  float *l_q = nullptr, *l_vfirst = nullptr, *l_cross = nullptr;
+  int32_t *d_row_seq = nullptr, *d_row_first = nullptr, *d_row_end = nullptr;
+  bool l_has_state = false;          // some layer keeps per-sequence state besides the cache (convolution rings)
   float* l_attn_scratch = nullptr;   // key splits of a decode step's latent attention
   bf16* l_xperm = nullptr;           // prompt-sized steps: the feed-forward input rows in expert (slot) order
   float* l_upf = nullptr;            // ... and the experts' up-projection sums before the activation
@@ -842,7 +855,34 @@ int forward_layers(b2_engine* e, const Lane& ln, int T, int ntiles) {
 // layer share one statistic (one kernel).  Mixer = latent attention in absorbed form (attn_latent.cu); feed-forward =
 // routed squared-ReLU experts as ragged groups of gemm_any.cu.  `rows` (device, nlast entries; null = every row) selects
 // the positions that get logits.  Operands are bf16, or fp32 when the engine was created with compute_f32.
-constexpr int LIST_TC_EXPERT_ROWS = 2048;   // (token, choice) pairs of a step from which the experts' products go expert by expert to the tcgen05 kernel
+constexpr int LIST_TC_EXPERT_ROWS = 2048;
+
+// C (fp32 [M][N]) = alpha * A (operand type [M][K]) . Wt^T for the layer-list families.  Prompt-sized bf16 products whose K the tcgen05
+// projection kernel can tile (gemm_tc.cu: TMA needs 16-byte rows, its k-block is 64) take that kernel, fp32 sums written directly;
+// everything else -- decode steps, fp32 mode, odd shapes -- takes gemm_any.cu.
+bool list_use_tc() {
+  static const bool use_tc = [] { const char* v = getenv("B2_LIST_TC"); return !(v && *v == '0'); }();
+  return use_tc;
+}
+int list_dense(b2_engine* e, const void* A, const void* Wt, float* C, int M, int N, int K, float alpha) {
+  const int f = e->f32 ? 1 : 0;
+  if (list_use_tc() && !f && alpha == 1.f && M > 64 && N >= 128 && K % 64 == 0) {
+    TcGemmArgs a;
+    a.bn = tc_pick_bn(M);
+    B2_TRY(b2_make_tmap_bf16(&a.tmap_w, Wt, (uint64_t)N, (uint64_t)K, (uint64_t)K, 128));
+    B2_TRY(b2_make_tmap_bf16(&a.tmap_x, A, (uint64_t)M, (uint64_t)K, (uint64_t)K, (uint32_t)a.bn));
+    a.T = M; a.N = N; a.K = K;
+    a.nsplit = 1;
+    a.out = C;
+    a.x_raw = A;
+    a.argmax_packed = nullptr;
+    a.epilogue = TC_EPI_F32_PARTIAL;
+    return launch_linear_tc(a, e->stream);
+  }
+  AnyGemm a;
+  a.A = A; a.W = Wt; a.C = C; a.M = M; a.N = N; a.K = K; a.lda = K; a.ldw = K; a.ldc = N; a.alpha = alpha;
+  return launch_gemm_any(a, f, f, 1, 1, 0, e->stream);
+}   // (token, choice) pairs of a step from which the experts' products go expert by expert to the tcgen05 kernel
 
 int forward_list(b2_engine* e, int T, int ntiles, int nlast) {
   const b2_config& c = e->cfg;
@@ -858,28 +898,8 @@ int forward_list(b2_engine* e, int T, int ntiles, int nlast) {
   }
   dbg(0);
   const PrefillTile* tiles = ntiles > 0 ? e->d_tiles : nullptr;
-  // C (fp32 [M][N]) = A (operand type [M][K]) . Wt^T.  Prompt-sized bf16 products whose K the tcgen05 projection kernel can
-  // tile (gemm_tc.cu: TMA needs 16-byte rows, its k-block is 64) take that kernel, fp32 sums written directly; everything else
-  // -- decode steps, fp32 mode, odd shapes -- takes gemm_any.cu.
-  static const bool use_tc = [] { const char* v = getenv("B2_LIST_TC"); return !(v && *v == '0'); }();
-  auto dense = [&](const void* A, const void* Wt, float* C, int M, int N, int K, float alpha) -> int {
-    if (use_tc && !f && alpha == 1.f && M > 64 && N >= 128 && K % 64 == 0) {
-      TcGemmArgs a;
-      a.bn = tc_pick_bn(M);
-      B2_TRY(b2_make_tmap_bf16(&a.tmap_w, Wt, (uint64_t)N, (uint64_t)K, (uint64_t)K, 128));
-      B2_TRY(b2_make_tmap_bf16(&a.tmap_x, A, (uint64_t)M, (uint64_t)K, (uint64_t)K, (uint32_t)a.bn));
-      a.T = M; a.N = N; a.K = K;
-      a.nsplit = 1;
-      a.out = C;
-      a.x_raw = A;
-      a.argmax_packed = nullptr;
-      a.epilogue = TC_EPI_F32_PARTIAL;
-      return launch_linear_tc(a, st);
-    }
-    AnyGemm a;
-    a.A = A; a.W = Wt; a.C = C; a.M = M; a.N = N; a.K = K; a.lda = K; a.ldw = K; a.ldc = N; a.alpha = alpha;
-    return launch_gemm_any(a, f, f, 1, 1, 0, st);
-  };
+  const bool use_tc = list_use_tc();
+  auto dense = [&](const void* A, const void* Wt, float* C, int M, int N, int K, float alpha) -> int { return list_dense(e, A, Wt, C, M, N, K, alpha); };
   for (int l = 0; l < c.num_layers; ++l) {
     ListLayer& L = e->ll[l];
     const b2_layer_spec& sp = L.sp;
@@ -1013,6 +1033,106 @@ int forward_list(b2_engine* e, int T, int ntiles, int nlast) {
   return 0;
 }
 
+// Kedasun: h <- h + n1b(mixer(n1(h))), then h <- h + n2b(ff(n2(h))) on the same fp32 residual stream, every norm an RMS norm over
+// equal pieces of the vector.  Mixers keep per-head keys and values (attn_heads.cu): q | k | v (| head gates) are ONE projection, the
+// kernel behind it finishes the token (bias, convolution, rotary or unit norm, value mixing, cache rows), attention runs over the
+// block table, and the norm behind the output projection adds into the stream.  Per-sequence state besides the cache (the
+// convolution's last projected rows) lives in rings indexed by the sequence slot.
+constexpr float KEDASUN_SLOPE_EXP = 8.0f;      // distance penalty of head a: 2^(-8 (a + 1) / heads) per position
+constexpr float KEDASUN_GATE_SHARP = 1.702f;   // y = g * sigmoid(1.702 g) * (u + 1)
+
+int forward_heads_list(b2_engine* e, int T, int ntiles, int nlast) {
+  const b2_config& c = e->cfg;
+  const int W = c.hidden, f = e->f32 ? 1 : 0, groups = c.norm_groups > 0 ? c.norm_groups : 1;
+  cudaStream_t st = e->stream;
+  auto dbg = [&](int slot) {
+    if ((e->debug_flags & 1) && e->dbg_hidden_f32 != nullptr && T <= e->dbg_cap_tokens)
+      cudaMemcpyAsync(e->dbg_hidden_f32 + (size_t)slot * e->dbg_cap_tokens * W, e->l_h, (size_t)T * W * 4, cudaMemcpyDeviceToDevice, st);
+  };
+  {
+    KL k(e, B2K_EMBED);
+    if (!k.skip()) B2_TRY(launch_embed_scaled(e->d_tokens, e->l_embed, f, c.embed_scale != 0.f ? c.embed_scale : 1.f, e->l_h, T, W, c.vocab, st));
+  }
+  dbg(0);
+  const PrefillTile* tiles = ntiles > 0 ? e->d_tiles : nullptr;
+  for (int l = 0; l < c.num_layers; ++l) {
+    ListLayer& L = e->ll[l];
+    const b2_layer_spec& sp = L.sp;
+    const bool conv = sp.mixer == B2_MIXER_CONV_ATTENTION;
+    HeadsGeom g{sp.heads, sp.kv_heads, sp.dim, sp.vdim, sp.rot_dims, sp.rot_base, sp.scale, c.rms_eps, conv ? sp.conv_taps : 0, conv ? 1 : 0,
+                conv ? 1 : 0, KEDASUN_SLOPE_EXP, sp.window, sp.keep_first, conv ? 1 : 0};
+    char* kc = e->regions[L.cache_region].base;
+    char* vc = e->regions[L.v_region].base;
+    {
+      KL k(e, B2K_NORM);
+      if (!k.skip()) B2_TRY(launch_group_norm(e->l_h, L.gain1, e->l_x1, f, T, W, groups, c.rms_eps, nullptr, st));
+    }
+    {
+      KL k(e, B2K_GEMM_QKV);  // q | k | v and, for the gated mixer, one gate logit per head: one projection
+      if (!k.skip()) B2_TRY(list_dense(e, e->l_x1, L.wqd, e->l_qd, T, L.nqd, W, 1.f));
+    }
+    {
+      KL k(e, B2K_ROPE_KV);
+      if (!k.skip()) B2_TRY(launch_heads_finish(e->l_qd, L.nqd, g, L.qkv_bias, L.conv_w, L.conv_ring, e->d_row_seq, e->d_row_first, e->d_row_end,
+                                                e->d_positions, e->d_slots, L.vmix_mode, L.vmix, e->l_vfirst, e->l_q, kc, vc, f, T, st));
+    }
+    {
+      KL k(e, ntiles > 0 ? B2K_MISC : B2K_ATTN_DECODE);
+      if (!k.skip()) B2_TRY(launch_heads_attention(e->l_q, kc, vc, f, g, e->d_block_table, e->bt_stride, c.block_size, tiles, ntiles, e->d_positions,
+                                                   e->d_seq_lens, conv ? (void*)e->l_cross : e->l_av, conv ? 1 : f, T, st));
+    }
+    if (conv) {
+      KL k(e, B2K_ACT);  // the heads' weights mixed (as sums over the per-head outputs) and the head gates
+      if (!k.skip()) B2_TRY(launch_talk_gate(e->l_cross, L.talk, e->l_qd + (L.nq + L.nk + L.nv), L.nqd, e->l_av, f, sp.heads, sp.kv_heads, sp.vdim, T, st));
+    }
+    {
+      KL k(e, B2K_GEMM_O);
+      if (!k.skip()) B2_TRY(list_dense(e, e->l_av, L.wo, e->l_mix, T, W, sp.heads * sp.vdim, 1.f));
+    }
+    {
+      KL k(e, B2K_NORM);  // h += n1b(mixer output + bias)
+      if (!k.skip()) B2_TRY(launch_group_norm_add(e->l_h, e->l_mix, L.o_bias, L.gain1b, T, W, groups, c.rms_eps, st));
+    }
+    if (sp.ff == B2_FF_CLAMPED_GATED) {
+      {
+        KL k(e, B2K_NORM);
+        if (!k.skip()) B2_TRY(launch_group_norm(e->l_h, L.gain2, e->l_x1, f, T, W, groups, c.rms_eps, nullptr, st));
+      }
+      {
+        KL k(e, B2K_GEMM_GATEUP);  // gate | up: one projection
+        if (!k.skip()) B2_TRY(list_dense(e, e->l_x1, L.up, e->l_y, T, 2 * sp.ff_dim, W, 1.f));
+      }
+      {
+        KL k(e, B2K_ACT);
+        if (!k.skip()) B2_TRY(launch_clamped_gate(e->l_y, e->l_act, f, T, sp.ff_dim, sp.ff_limit, KEDASUN_GATE_SHARP, st));
+      }
+      {
+        KL k(e, B2K_GEMM_DOWN);
+        if (!k.skip()) B2_TRY(list_dense(e, e->l_act, L.down, e->l_mix, T, W, sp.ff_dim, 1.f));
+      }
+      {
+        KL k(e, B2K_NORM);
+        if (!k.skip()) B2_TRY(launch_group_norm_add(e->l_h, e->l_mix, nullptr, L.gain2b, T, W, groups, c.rms_eps, st));
+      }
+    }
+    dbg(l + 1);
+  }
+  {
+    KL k(e, B2K_NORM);
+    if (!k.skip()) B2_TRY(launch_group_norm(e->l_h, e->l_final_gain, e->l_xl, f, nlast, W, groups, c.rms_eps, ntiles > 0 ? e->d_last_rows : nullptr, st));
+  }
+  {
+    KL k(e, B2K_LMHEAD);
+    if (!k.skip()) B2_TRY(list_dense(e, e->l_xl, e->l_head, e->l_logits, nlast, c.vocab, W, 1.f));
+  }
+  {
+    KL k(e, B2K_MISC);
+    bf16* lb = (e->debug_flags & 2) ? e->logits : nullptr;
+    if (!k.skip()) B2_TRY(launch_logits_finish(e->l_logits, e->d_out_tokens, lb, bucket_batch(std::max(c.max_seqs, 1)), nlast, c.vocab, e->v_pad, st));
+  }
+  return 0;
+}
+
 // Two-lane decode.  At batch 64 a decode step is two things that do not overlap when they depend on each other: the
 // attention pass of a layer (HBM-bound, about half the step) and the eight small kernels between two attention
 // passes (a chain of dependent launches that moves 31 MB of weights in ~30 us: latency-bound, HBM nearly idle).
@@ -1032,6 +1152,7 @@ int forward(b2_engine* e, int T, int ntiles, int nlast, int attn_split) {
   const int H = c.hidden;
   (void)attn_split;
   if (c.arch == B2_ARCH_LERASUN) return forward_list(e, T, ntiles, nlast);
+  if (c.arch == B2_ARCH_KEDASUN) return forward_heads_list(e, T, ntiles, nlast);
   if (c.arch == B2_ARCH_OPT) return forward_opt(e, T, ntiles, nlast);
   if (ntiles == 0 && e->use_chain == 2 && e->fused_ok && c.arch == B2_ARCH_QWEN3 && !(e->debug_flags & 1) &&
       e->force_gemm_impl != 0 && T > e->simt_max_tokens && T <= 64 && e->skip_mask == 0)
@@ -1211,7 +1332,7 @@ int run_decode_step(b2_engine* e, int B, int attn_split) {
 // advance kernel at the head of the step brings them to the position of the appended token.
 int upload_decode_batch(b2_engine* e, int n, const int32_t* seq_ids, int B) {
   const int bs = e->cfg.block_size;
-  size_t need = (size_t)3 * B + (size_t)B * e->bt_stride;
+  size_t need = (size_t)6 * B + (size_t)B * e->bt_stride;
   if (need > e->h_stage_ints) {
     b2_set_error("decode batch of %d does not fit the staging buffer", B);
     return -12;
@@ -1239,6 +1360,17 @@ int upload_decode_batch(b2_engine* e, int n, const int32_t* seq_ids, int B) {
   B2_CUDA_OK(cudaMemcpyAsync(e->d_seq_lens, lens, B * 4, cudaMemcpyHostToDevice, e->stream));
   B2_CUDA_OK(cudaMemcpyAsync(e->d_slots, slots, B * 4, cudaMemcpyHostToDevice, e->stream));
   B2_CUDA_OK(cudaMemcpyAsync(e->d_block_table, bt, (size_t)B * e->bt_stride * 4, cudaMemcpyHostToDevice, e->stream));
+  if (e->d_row_seq) {  // every row is a portion of one token of its own sequence slot
+    int32_t* rs = bt + (size_t)B * e->bt_stride;
+    for (int i = 0; i < B; ++i) {
+      rs[i] = i < n ? seq_ids[i] : 0;
+      rs[B + i] = i;
+      rs[2 * B + i] = i + 1;
+    }
+    B2_CUDA_OK(cudaMemcpyAsync(e->d_row_seq, rs, B * 4, cudaMemcpyHostToDevice, e->stream));
+    B2_CUDA_OK(cudaMemcpyAsync(e->d_row_first, rs + B, B * 4, cudaMemcpyHostToDevice, e->stream));
+    B2_CUDA_OK(cudaMemcpyAsync(e->d_row_end, rs + 2 * B, B * 4, cudaMemcpyHostToDevice, e->stream));
+  }
   B2_CUDA_OK(cudaStreamSynchronize(e->stream));  // staging buffer is reused
   e->cur_batch.assign(seq_ids, seq_ids + n);
   e->cur_B = B;
@@ -1405,7 +1537,7 @@ int list_tensor(b2_engine* e, const std::string& name, const void* host, size_t 
   if (name == "embed") { B2_TRY(want((size_t)c.vocab * W)); return done(put_operand(e, e->l_embed, 0, src, (size_t)c.vocab * W)); }
   if (name == "head") { B2_TRY(want((size_t)c.vocab * W)); return done(put_operand(e, e->l_head, 0, src, (size_t)c.vocab * W)); }
   if (name == "embed.norm") { B2_TRY(want(W)); return done(put_f32(e->l_embed_gain, src, W, 1.0f)); }
-  if (name == "final.norm") { B2_TRY(want(W)); return done(put_f32(e->l_final_gain, src, W, 1.0f)); }
+  if (name == "final.norm") { B2_TRY(want(W)); return done(put_f32(e->l_final_gain, src, W, c.arch == B2_ARCH_KEDASUN ? 0.0f : 1.0f)); }
   size_t dot = name.find('.');
   if (name.size() < 3 || name[0] != 'l' || dot == std::string::npos || dot < 2) {
     b2_set_error("unknown tensor name %s", name.c_str());
@@ -1420,6 +1552,37 @@ int list_tensor(b2_engine* e, const std::string& name, const void* host, size_t 
   const b2_layer_spec& sp = L.sp;
   const std::string rest = name.substr(dot + 1);
   const size_t H = sp.heads, dn = sp.dim, dr = sp.rot_dim, dv = sp.vdim, r = sp.kv_rank, ff = sp.ff_dim;
+  if (c.arch == B2_ARCH_KEDASUN) {
+    const size_t nq = L.nq, nk = L.nk, nv = L.nv, taps = sp.conv_taps;
+    const bool conv = sp.mixer == B2_MIXER_CONV_ATTENTION;
+    if (rest == "norm1") { B2_TRY(want(W)); return done(put_f32(L.gain1, src, W, 0.0f)); }
+    if (rest == "norm1b") { B2_TRY(want(W)); return done(put_f32(L.gain1b, src, W, 0.0f)); }
+    if (rest == "norm2" && L.gain2) { B2_TRY(want(W)); return done(put_f32(L.gain2, src, W, 0.0f)); }
+    if (rest == "norm2b" && L.gain2b) { B2_TRY(want(W)); return done(put_f32(L.gain2b, src, W, 0.0f)); }
+    if (rest == "mix.q") { B2_TRY(want(nq * W)); return done(put_operand(e, L.wqd, 0, src, nq * W)); }
+    if (rest == "mix.k") { B2_TRY(want(nk * W)); return done(put_operand(e, L.wqd, nq * W, src, nk * W)); }
+    if (rest == "mix.v") { B2_TRY(want(nv * W)); return done(put_operand(e, L.wqd, (nq + nk) * W, src, nv * W)); }
+    if (rest == "mix.o") { B2_TRY(want(W * H * dv)); return done(put_operand(e, L.wo, 0, src, W * H * dv)); }
+    if (rest == "mix.vmix") { B2_TRY(want(1)); return done(put_f32(L.vmix, src, 1, 0.0f)); }
+    if (conv) {
+      if (rest == "mix.g") { B2_TRY(want(H * W)); return done(put_operand(e, L.wqd, (nq + nk + nv) * W, src, H * W)); }
+      if (rest == "mix.q.b") { B2_TRY(want(nq)); return done(put_f32(L.qkv_bias, src, nq, 0.0f)); }
+      if (rest == "mix.k.b") { B2_TRY(want(nk)); return done(put_f32(L.qkv_bias + nq, src, nk, 0.0f)); }
+      if (rest == "mix.v.b") { B2_TRY(want(nv)); return done(put_f32(L.qkv_bias + nq + nk, src, nv, 0.0f)); }
+      if (rest == "mix.o.b") { B2_TRY(want(W)); return done(put_f32(L.o_bias, src, W, 0.0f)); }
+      if (rest == "mix.q.conv") { B2_TRY(want(nq * taps)); return done(put_f32(L.conv_w, src, nq * taps, 0.0f)); }
+      if (rest == "mix.k.conv") { B2_TRY(want(nk * taps)); return done(put_f32(L.conv_w + nq * taps, src, nk * taps, 0.0f)); }
+      if (rest == "mix.v.conv") { B2_TRY(want(nv * taps)); return done(put_f32(L.conv_w + (nq + nk) * taps, src, nv * taps, 0.0f)); }
+      if (rest == "mix.talk") { B2_TRY(want(H * H)); return done(put_f32(L.talk, src, H * H, 0.0f)); }
+    }
+    if (sp.ff == B2_FF_CLAMPED_GATED) {
+      if (rest == "mlp.gate") { B2_TRY(want(ff * W)); return done(put_operand(e, L.up, 0, src, ff * W)); }
+      if (rest == "mlp.up") { B2_TRY(want(ff * W)); return done(put_operand(e, L.up, ff * W, src, ff * W)); }
+      if (rest == "mlp.down") { B2_TRY(want(W * ff)); return done(put_operand(e, L.down, 0, src, W * ff)); }
+    }
+    b2_set_error("unknown tensor name %s", name.c_str());
+    return -22;
+  }
   if (rest == "norm1") { B2_TRY(want(W)); return done(put_f32(L.gain1, src, W, 1.0f)); }
   if (rest == "norm2" && L.gain2) { B2_TRY(want(W)); return done(put_f32(L.gain2, src, W, 1.0f)); }
   if (rest == "mix.q") { B2_TRY(want((size_t)L.nq * W)); return done(put_operand(e, L.wqd, 0, src, (size_t)L.nq * W)); }
@@ -1454,6 +1617,15 @@ int list_tensor(b2_engine* e, const std::string& name, const void* host, size_t 
 }
 
 int list_tensor_count(const b2_engine* e) {
+  if (e->cfg.arch == B2_ARCH_KEDASUN) {
+    int n = 3;  // embed, head, final.norm
+    for (const ListLayer& L : e->ll) {
+      n += 2 + 5;                                               // norm1, norm1b; q, k, v, o, vmix
+      if (L.sp.mixer == B2_MIXER_CONV_ATTENTION) n += 4 + 3 + 2;  // biases of q, k, v, o; their convolutions; talk, g
+      if (L.sp.ff == B2_FF_CLAMPED_GATED) n += 2 + 3;           // norm2, norm2b; gate, up, down
+    }
+    return n;
+  }
   int n = 4;
   for (const ListLayer& L : e->ll) {
     n += 1 + 5 + (L.sp.kv_from < 0 ? 2 : 0);  // norm1; q, uk, uv, sink, o; dkv, dkv.norm
@@ -1462,8 +1634,117 @@ int list_tensor_count(const b2_engine* e) {
   return n;
 }
 
+// The same for the family whose mixers keep per-head keys and values (Kedasun).
+int heads_engine_alloc(b2_engine* e) {
+  const b2_config& c = e->cfg;
+  const size_t W = c.hidden, es = e->esz;
+  B2_REQUIRE(!e->specs.empty() && (int)e->specs.size() == c.num_layers, "Kedasun: layer_specs missing");
+  B2_REQUIRE(c.hidden >= 1 && c.vocab >= 1 && c.num_layers >= 1, "Kedasun: bad sizes");
+  const int groups = c.norm_groups > 0 ? c.norm_groups : 1;
+  B2_REQUIRE(c.hidden % groups == 0, "Kedasun: width %d is not %d equal norm pieces", c.hidden, groups);
+  auto xalloc = [&](void** p, size_t elems) -> int {
+    char* q = nullptr;
+    B2_TRY(dalloc(&q, std::max<size_t>(elems, 1) * es));
+    *p = q;
+    e->weight_bytes += (int64_t)(elems * es);
+    return 0;
+  };
+  auto falloc = [&](float** p, size_t n) -> int {
+    B2_TRY(dalloc(p, std::max<size_t>(n, 1)));
+    B2_CUDA_OK(cudaMemset(*p, 0, std::max<size_t>(n, 1) * 4));
+    e->weight_bytes += (int64_t)(n * 4);
+    return 0;
+  };
+  e->weight_bytes = 0;
+  B2_TRY(xalloc(&e->l_embed, (size_t)c.vocab * W));
+  B2_TRY(xalloc(&e->l_head, (size_t)c.vocab * W));
+  B2_TRY(falloc(&e->l_final_gain, W));
+  e->ll.resize(c.num_layers);
+  size_t max_nqd = 1, max_nq = 1, max_nv = 1, max_hv = 1, max_cross = 0, max_ff = 1;
+  int first_vmix = -1;
+  for (int l = 0; l < c.num_layers; ++l) {
+    ListLayer& L = e->ll[l];
+    L.sp = e->specs[l];
+    const b2_layer_spec& sp = L.sp;
+    const bool conv = sp.mixer == B2_MIXER_CONV_ATTENTION;
+    B2_REQUIRE(sp.mixer == B2_MIXER_ATTENTION || conv, "layer %d: mixer kind %d not built for this family", l, sp.mixer);
+    B2_REQUIRE(sp.heads >= 1 && sp.kv_heads >= 1 && sp.heads % sp.kv_heads == 0 && sp.dim >= 1 && sp.vdim >= 1,
+               "layer %d: bad mixer sizes (heads %d, kv_heads %d, dim %d, vdim %d)", l, sp.heads, sp.kv_heads, sp.dim, sp.vdim);
+    B2_REQUIRE(sp.rot_dims >= 0 && sp.rot_dims <= sp.dim && sp.rot_dims % 2 == 0, "layer %d: rot dims %d must be even and <= dim %d", l, sp.rot_dims, sp.dim);
+    B2_REQUIRE(!conv || sp.conv_taps >= 1, "layer %d: the convolution needs at least one tap", l);
+    B2_REQUIRE(sp.window >= 0 && sp.keep_first >= 0, "layer %d: bad window", l);
+    B2_REQUIRE(sp.ff == B2_FF_NONE || (sp.ff == B2_FF_CLAMPED_GATED && sp.ff_dim >= 1), "layer %d: feed-forward kind %d not built for this family", l, sp.ff);
+    L.nq = sp.heads * sp.dim;
+    L.nk = sp.kv_heads * sp.dim;
+    L.nv = sp.kv_heads * sp.vdim;
+    L.nqd = L.nq + L.nk + L.nv + (conv ? sp.heads : 0);
+    if (sp.v_mix) {
+      if (first_vmix < 0) first_vmix = l;
+      B2_REQUIRE(e->ll[first_vmix].nv == L.nv, "layer %d: value mixing needs the value sizes of layer %d", l, first_vmix);
+      L.vmix_mode = first_vmix == l ? 1 : 2;
+    }
+    B2_TRY(xalloc(&L.wqd, (size_t)L.nqd * W));
+    B2_TRY(xalloc(&L.wo, W * sp.heads * sp.vdim));
+    B2_TRY(falloc(&L.gain1, W));
+    B2_TRY(falloc(&L.gain1b, W));
+    B2_TRY(falloc(&L.vmix, 1));
+    if (conv) {
+      const size_t C = (size_t)L.nq + L.nk + L.nv;
+      B2_TRY(falloc(&L.qkv_bias, C));
+      B2_TRY(falloc(&L.o_bias, W));
+      B2_TRY(falloc(&L.conv_w, C * sp.conv_taps));
+      B2_TRY(falloc(&L.talk, (size_t)sp.heads * sp.heads));
+      B2_TRY(dalloc(&L.conv_ring, (size_t)c.max_seqs * sp.conv_taps * C));
+      e->l_has_state = e->l_has_state || sp.conv_taps > 1;
+      max_cross = std::max(max_cross, (size_t)sp.heads * L.nv);
+    }
+    if (sp.ff == B2_FF_CLAMPED_GATED) {
+      B2_TRY(falloc(&L.gain2, W));
+      B2_TRY(falloc(&L.gain2b, W));
+      B2_TRY(xalloc(&L.up, (size_t)2 * sp.ff_dim * W));
+      B2_TRY(xalloc(&L.down, W * sp.ff_dim));
+      max_ff = std::max(max_ff, (size_t)sp.ff_dim);
+    }
+    max_nqd = std::max(max_nqd, (size_t)L.nqd);
+    max_nq = std::max(max_nq, (size_t)L.nq);
+    max_nv = std::max(max_nv, (size_t)L.nv);
+    max_hv = std::max(max_hv, (size_t)sp.heads * sp.vdim);
+  }
+  e->cap_tokens = ((std::max(c.max_batch_tokens, c.max_seqs) + 255) / 256) * 256;
+  const size_t Tc = e->cap_tokens;
+  e->l_rows_cap = (int)(Tc + bucket_batch(c.max_seqs));
+  e->l_max_top = 1;
+  e->v_pad = (c.vocab + 7) / 8 * 8;
+  auto aalloc = [&](void** p, size_t elems) -> int {
+    char* q = nullptr;
+    B2_TRY(dalloc(&q, elems * es));
+    *p = q;
+    return 0;
+  };
+  B2_TRY(dalloc(&e->l_h, Tc * W));
+  B2_TRY(dalloc(&e->l_qd, Tc * max_nqd));
+  B2_TRY(dalloc(&e->l_q, Tc * max_nq));
+  B2_TRY(dalloc(&e->l_vfirst, Tc * max_nv));
+  if (max_cross > 0) B2_TRY(dalloc(&e->l_cross, Tc * max_cross));
+  B2_TRY(dalloc(&e->l_mix, Tc * W));
+  B2_TRY(dalloc(&e->l_y, Tc * 2 * max_ff));
+  B2_TRY(dalloc(&e->l_logits, (size_t)e->l_rows_cap * c.vocab));
+  B2_TRY(aalloc(&e->l_x1, Tc * W));
+  B2_TRY(aalloc(&e->l_av, Tc * max_hv));
+  B2_TRY(aalloc(&e->l_act, Tc * max_ff));
+  B2_TRY(aalloc(&e->l_xl, (size_t)e->l_rows_cap * W));
+  B2_TRY(dalloc(&e->d_row_seq, Tc));
+  B2_TRY(dalloc(&e->d_row_first, Tc));
+  B2_TRY(dalloc(&e->d_row_end, Tc));
+  B2_CUDA_OK(cudaMemset(e->d_row_seq, 0, Tc * 4));
+  B2_CUDA_OK(cudaMemset(e->d_row_first, 0, Tc * 4));
+  B2_CUDA_OK(cudaMemset(e->d_row_end, 0, Tc * 4));
+  return 0;
+}
+
 // Validates the layer list and allocates weights, activations and scratch of a layer-list engine.
 int list_engine_alloc(b2_engine* e) {
+  if (e->cfg.arch == B2_ARCH_KEDASUN) return heads_engine_alloc(e);
   const b2_config& c = e->cfg;
   const size_t W = c.hidden, es = e->esz;
   B2_REQUIRE(!e->specs.empty() && (int)e->specs.size() == c.num_layers, "Lerasun: layer_specs missing");
@@ -1587,7 +1868,7 @@ int list_engine_alloc(b2_engine* e) {
 
 int layer_tensor(b2_engine* e, const std::string& name, const void* host, size_t nbytes) {
   const b2_config& c = e->cfg;
-  if (c.arch == B2_ARCH_LERASUN) return list_tensor(e, name, host, nbytes);
+  if (list_arch(c.arch)) return list_tensor(e, name, host, nbytes);
   const int H = c.hidden, I = c.intermediate;
   auto put = [&](bf16* dst, size_t elems) -> int {
     if (nbytes != elems * 2) {
@@ -1840,11 +2121,11 @@ int load_safetensors(b2_engine* e, const char* path) {
 extern "C" int b2_engine_create(const b2_config* cfg, const char* safetensors_path, int device, b2_engine** out) {
   B2_REQUIRE(cfg != nullptr && out != nullptr, "b2_engine_create: null argument");
   B2_REQUIRE(cfg->abi_version == B2_ABI_VERSION, "b2_engine_create: abi_version %d != %d", cfg->abi_version, B2_ABI_VERSION);
-  B2_REQUIRE(cfg->arch == B2_ARCH_QWEN3 || cfg->arch == B2_ARCH_PHI3 || cfg->arch == B2_ARCH_OPT || cfg->arch == B2_ARCH_LERASUN,
-             "arch %d not built (0 = Qwen3, 1 = Phi-3, 2 = OPT, 3 = Lerasun)", cfg->arch);
-  const bool ls = cfg->arch == B2_ARCH_LERASUN;  // a layer-list family: its sizes live in layer_specs and are checked in list_engine_alloc
-  B2_REQUIRE(ls || !cfg->compute_f32, "compute_f32: only the Lerasun family has an fp32 path");
-  B2_REQUIRE(!ls || cfg->layer_specs != nullptr, "Lerasun: layer_specs is NULL");
+  B2_REQUIRE(cfg->arch == B2_ARCH_QWEN3 || cfg->arch == B2_ARCH_PHI3 || cfg->arch == B2_ARCH_OPT || list_arch(cfg->arch),
+             "arch %d not built (0 = Qwen3, 1 = Phi-3, 2 = OPT, 3 = Lerasun, 4 = Kedasun)", cfg->arch);
+  const bool ls = list_arch(cfg->arch);  // a layer-list family: its sizes live in layer_specs and are checked in list_engine_alloc
+  B2_REQUIRE(ls || !cfg->compute_f32, "compute_f32: only the layer-list families have an fp32 path");
+  B2_REQUIRE(!ls || cfg->layer_specs != nullptr, "layer-list family: layer_specs is NULL");
   B2_REQUIRE(cfg->arch != B2_ARCH_OPT || cfg->tie_embeddings, "OPT: the lm_head is tied to embed_tokens");
   B2_REQUIRE(cfg->sliding_window >= 0 && (cfg->sliding_window == 0 || cfg->arch == B2_ARCH_PHI3),
              "sliding_window %d: only the Phi-3 family has one", cfg->sliding_window);
@@ -2093,7 +2374,7 @@ extern "C" int b2_engine_create(const b2_config* cfg, const char* safetensors_pa
     E_CUDA(cudaMemset(e->d_block_table, 0, Bcap * e->bt_stride * 4));
     e->tiles_cap = (int)(Tc / 64 + 2 * Bcap + 16);
     E_TRY(dalloc(&e->d_tiles, (size_t)e->tiles_cap));
-    e->h_stage_ints = std::max((size_t)4 * Tc + Bcap * (size_t)e->bt_stride + 5 * Bcap, (size_t)1 << 16);
+    e->h_stage_ints = std::max((size_t)7 * Tc + Bcap * (size_t)e->bt_stride + 8 * Bcap, (size_t)1 << 16);
     E_CUDA(cudaMallocHost(&e->h_stage, e->h_stage_ints * sizeof(int32_t)));
     E_CUDA(cudaMallocHost(&e->h_tiles, (size_t)e->tiles_cap * sizeof(PrefillTile)));
     E_CUDA(cudaMallocHost(&e->h_out, (size_t)e->log_cap_steps * c.max_seqs * sizeof(int32_t)));
@@ -2105,10 +2386,13 @@ extern "C" int b2_engine_create(const b2_config* cfg, const char* safetensors_pa
       const size_t blk_elems = (size_t)e->nkv * c.block_size * e->hd;
       // bytes one page takes in all regions together
       size_t page_bytes_all = blk_elems * 2 * 2 * c.num_layers;
+      const bool heads_cache = c.arch == B2_ARCH_KEDASUN;  // a K region and a V region per layer, rows of kv_heads * dim / kv_heads * vdim
       if (ls) {
         page_bytes_all = 0;
-        for (const ListLayer& L : e->ll)
-          if (L.sp.kv_from < 0) page_bytes_all += (size_t)c.block_size * (L.sp.kv_rank + L.sp.rot_dim) * e->esz;
+        for (const ListLayer& L : e->ll) {
+          if (heads_cache) page_bytes_all += (size_t)c.block_size * (L.nk + L.nv) * e->esz;
+          else if (L.sp.kv_from < 0) page_bytes_all += (size_t)c.block_size * (L.sp.kv_rank + L.sp.rot_dim) * e->esz;
+        }
       }
       int64_t nb = c.num_blocks;
       if (nb <= 0) {
@@ -2130,6 +2414,16 @@ extern "C" int b2_engine_create(const b2_config* cfg, const char* safetensors_pa
         E_CUDA(cudaMemset(e->l_pool, 0, (size_t)nb * page_bytes_all));
         size_t off = 0;
         for (ListLayer& L : e->ll) {
+          if (heads_cache) {
+            const size_t kb = (size_t)c.block_size * L.nk * e->esz, vb = (size_t)c.block_size * L.nv * e->esz;
+            L.cache_region = (int)e->regions.size();
+            e->regions.push_back({e->l_pool + off, kb});
+            off += (size_t)nb * kb;
+            L.v_region = (int)e->regions.size();
+            e->regions.push_back({e->l_pool + off, vb});
+            off += (size_t)nb * vb;
+            continue;
+          }
           if (L.sp.kv_from >= 0) continue;
           const size_t pb = (size_t)c.block_size * (L.sp.kv_rank + L.sp.rot_dim) * e->esz;
           L.cache_region = (int)e->regions.size();
@@ -2137,7 +2431,7 @@ extern "C" int b2_engine_create(const b2_config* cfg, const char* safetensors_pa
           off += (size_t)nb * pb;
         }
         for (ListLayer& L : e->ll)
-          if (L.sp.kv_from >= 0) L.cache_region = e->ll[L.sp.kv_from].cache_region;
+          if (!heads_cache && L.sp.kv_from >= 0) L.cache_region = e->ll[L.sp.kv_from].cache_region;
       } else {
         E_TRY(dalloc(&e->kv_pool, (size_t)2 * c.num_layers * e->layer_kv_elems));
         E_CUDA(cudaMemset(e->kv_pool, 0, (size_t)2 * c.num_layers * e->layer_kv_elems * 2));
@@ -2186,7 +2480,7 @@ extern "C" int b2_engine_load_safetensors(b2_engine* e, const char* path) {
 extern "C" int b2_engine_finalize(b2_engine* e) {
   B2_REQUIRE(e, "b2_engine_finalize: null engine");
   const int arch = e->cfg.arch;
-  if (arch == B2_ARCH_LERASUN) {
+  if (list_arch(arch)) {
     const int want = list_tensor_count(e);
     B2_REQUIRE((int)e->loaded.size() == want, "weights incomplete: %d of %d tensors loaded", (int)e->loaded.size(), want);
     e->finalized = true;
@@ -2233,10 +2527,12 @@ extern "C" void b2_engine_free(b2_engine* e) {
   F(e->partial2); F(e->attn_scratch2); F(e->ssq);
   F(e->l_embed); F(e->l_head); F(e->l_embed_gain); F(e->l_final_gain); F(e->l_pool); F(e->l_h); F(e->l_qd); F(e->l_qrot); F(e->l_qabs);
   F(e->l_xperm); F(e->l_upf); if (e->h_offsets) cudaFreeHost(e->h_offsets);
+  F(e->l_q); F(e->l_vfirst); F(e->l_cross); F(e->d_row_seq); F(e->d_row_first); F(e->d_row_end);
   F(e->l_mix); F(e->l_y); F(e->l_rw); F(e->l_logits); F(e->l_x1); F(e->l_x2); F(e->l_qnope); F(e->l_olat); F(e->l_av); F(e->l_act); F(e->l_xl);
   F(e->l_attn_scratch); F(e->l_idx); F(e->l_offsets); F(e->l_slot_token); F(e->l_pair_slot); F(e->l_tile_group); F(e->l_tile_row0); F(e->l_ntiles); F(e->dbg_hidden_f32);
   for (auto& L : e->ll) {
     F(L.wqd); F(L.ukT); F(L.uv); F(L.wo); F(L.up); F(L.down); F(L.gain1); F(L.gain2); F(L.lat_gain); F(L.sink); F(L.router); F(L.corr);
+    F(L.gain1b); F(L.gain2b); F(L.qkv_bias); F(L.o_bias); F(L.conv_w); F(L.talk); F(L.vmix); F(L.conv_ring);
   }
   if (e->ev_fork) cudaEventDestroy(e->ev_fork);
   if (e->ev_join) cudaEventDestroy(e->ev_join);
@@ -2331,6 +2627,9 @@ extern "C" int b2_seq_truncate(b2_engine* e, int32_t seq_id, int32_t new_len) {
   B2_TRY(check_seq(e, seq_id));
   Seq& s = e->seqs[seq_id];
   B2_REQUIRE(new_len >= 0 && new_len <= s.len, "b2_seq_truncate: new_len %d outside [0, %d]", new_len, s.len);
+  // State besides the cache (the convolutions' last projected rows) exists for the sequence's end only: it cannot be cut back
+  // to an earlier position, only kept (new_len == len) or started over (new_len == 0).
+  B2_REQUIRE(!e->l_has_state || new_len == s.len || new_len == 0, "b2_seq_truncate: this model keeps per-sequence state; a sequence can only be cut back to 0");
   // Positions >= new_len will be written again.  Pages from there on that are registered in the prefix cache or held by
   // other sequences too must not be: the sequence swaps them for private pages (copying the kept part of the page
   // new_len falls into), and its own chain ends at the cut.
@@ -2376,7 +2675,7 @@ extern "C" int b2_prefill(b2_engine* e, const int32_t* ids, const int32_t* seq_o
 extern "C" int b2_prefill_logits(b2_engine* e, const int32_t* ids, const int32_t* seq_offsets, int32_t nseq, const int32_t* seq_ids,
                                  const int32_t* rows, int32_t nrows, float* out_logits, int32_t* out_tokens) {
   B2_REQUIRE(e && nrows >= 0 && (nrows == 0 || (rows && out_logits)), "b2_prefill_logits: bad arguments");
-  B2_REQUIRE(e->cfg.arch == B2_ARCH_LERASUN, "b2_prefill_logits: built for the families whose lm_head writes fp32 rows (Lerasun)");
+  B2_REQUIRE(list_arch(e->cfg.arch), "b2_prefill_logits: built for the families whose lm_head writes fp32 rows (the layer-list families)");
   return prefill_impl(e, ids, seq_offsets, nseq, seq_ids, rows, nrows, out_logits, out_tokens);
 }
 namespace {
@@ -2423,6 +2722,9 @@ int prefill_impl(b2_engine* e, const int32_t* ids, const int32_t* seq_offsets, i
     B2_REQUIRE(rows[i] >= 0 && rows[i] < T_in, "b2_prefill_logits: row %d outside the call's %d tokens", rows[i], T_in);
     last[nseq + i] = rows[i];  // (no prefix-cache skip in this form: rows index the tokens as given)
   }
+  // families with per-sequence state besides the cache: every token row's sequence slot and the row range of its portion
+  int32_t* rowinfo = e->d_row_seq ? bt + (size_t)nseq * e->bt_stride : nullptr;
+  B2_REQUIRE(!rowinfo || (size_t)(rowinfo - e->h_stage) + (size_t)3 * T <= e->h_stage_ints, "b2_prefill: %d tokens exceed the staging buffer", T);
   int ntiles = 0, row0 = 0;
   for (int i = 0; i < nseq; ++i) {
     Seq& s = e->seqs[seq_ids[i]];
@@ -2434,6 +2736,12 @@ int prefill_impl(b2_engine* e, const int32_t* ids, const int32_t* seq_offsets, i
       pos[row0 + j] = p;
       slots[row0 + j] = s.blocks[p / bs] * bs + p % bs;
     }
+    if (rowinfo)
+      for (int j = 0; j < n; ++j) {
+        rowinfo[row0 + j] = seq_ids[i];
+        rowinfo[T + row0 + j] = row0;
+        rowinfo[2 * T + row0 + j] = row0 + n;
+      }
     last[i] = row0 + n - 1;
     memset(bt + (size_t)i * e->bt_stride, 0, (size_t)e->bt_stride * 4);
     memcpy(bt + (size_t)i * e->bt_stride, s.blocks.data(), s.blocks.size() * 4);
@@ -2454,6 +2762,11 @@ int prefill_impl(b2_engine* e, const int32_t* ids, const int32_t* seq_offsets, i
   B2_CUDA_OK(cudaMemcpyAsync(e->d_last_rows, last, (nseq + nrows) * 4, cudaMemcpyHostToDevice, e->stream));
   B2_CUDA_OK(cudaMemcpyAsync(e->d_block_table, bt, (size_t)nseq * e->bt_stride * 4, cudaMemcpyHostToDevice, e->stream));
   B2_CUDA_OK(cudaMemcpyAsync(e->d_tiles, e->h_tiles, ntiles * sizeof(PrefillTile), cudaMemcpyHostToDevice, e->stream));
+  if (rowinfo) {
+    B2_CUDA_OK(cudaMemcpyAsync(e->d_row_seq, rowinfo, T * 4, cudaMemcpyHostToDevice, e->stream));
+    B2_CUDA_OK(cudaMemcpyAsync(e->d_row_first, rowinfo + T, T * 4, cudaMemcpyHostToDevice, e->stream));
+    B2_CUDA_OK(cudaMemcpyAsync(e->d_row_end, rowinfo + 2 * T, T * 4, cudaMemcpyHostToDevice, e->stream));
+  }
   if (e->debug_flags & 2) B2_TRY(ensure_logits(e));
   e->cur_batch.clear();
   B2_TRY(forward(e, T, ntiles, nseq + nrows, 1));
@@ -2638,7 +2951,7 @@ extern "C" int b2_attn_profile(b2_engine* e, int32_t nseq, const int32_t* seq_id
                                int64_t* kv_bytes_per_launch) {
   B2_REQUIRE(e && seq_ids && reps >= 1 && ms_per_launch && kv_bytes_per_launch, "b2_attn_profile: bad arguments");
   B2_CUDA_OK(cudaSetDevice(e->device));
-  B2_REQUIRE(e->cfg.arch != B2_ARCH_LERASUN, "b2_attn_profile: times the GQA decode-attention kernel; this family has none");
+  B2_REQUIRE(!list_arch(e->cfg.arch), "b2_attn_profile: times the GQA decode-attention kernel; this family has none");
   B2_REQUIRE((int)e->cur_batch.size() == nseq && std::equal(seq_ids, seq_ids + nseq, e->cur_batch.begin()),
              "b2_attn_profile: run a decode step on exactly this batch first (the pass reuses its device-side page tables)");
   const b2_config& c = e->cfg;
@@ -2719,7 +3032,7 @@ extern "C" int b2_set_debug(b2_engine* e, int32_t flags) {
   B2_REQUIRE(e, "b2_set_debug: null engine");
   B2_CUDA_OK(cudaSetDevice(e->device));
   e->debug_flags = flags;
-  if ((flags & 1) && e->cfg.arch == B2_ARCH_LERASUN) {
+  if ((flags & 1) && list_arch(e->cfg.arch)) {
     if (e->dbg_hidden_f32 == nullptr) {
       e->dbg_cap_tokens = std::min(e->cap_tokens, 1024);
       B2_TRY(dalloc(&e->dbg_hidden_f32, (size_t)(e->cfg.num_layers + 1) * e->dbg_cap_tokens * e->cfg.hidden));
@@ -2734,7 +3047,7 @@ extern "C" int b2_set_debug(b2_engine* e, int32_t flags) {
 
 extern "C" int b2_get_hidden(b2_engine* e, int32_t layer, int32_t ntokens, uint16_t* out_bf16) {
   B2_REQUIRE(e && out_bf16, "b2_get_hidden: null argument");
-  B2_REQUIRE(e->cfg.arch != B2_ARCH_LERASUN, "b2_get_hidden: this family's residual stream is fp32 (b2_get_hidden_f32)");
+  B2_REQUIRE(!list_arch(e->cfg.arch), "b2_get_hidden: this family's residual stream is fp32 (b2_get_hidden_f32)");
   B2_REQUIRE((e->debug_flags & 1) && e->dbg_hidden, "b2_get_hidden: hidden capture not enabled (b2_set_debug(e, 1))");
   B2_REQUIRE(layer >= -1 && layer <= e->cfg.num_layers, "b2_get_hidden: layer %d out of range", layer);
   B2_REQUIRE(ntokens >= 1 && ntokens <= e->dbg_cap_tokens && ntokens <= e->last_tokens, "b2_get_hidden: ntokens %d out of range", ntokens);
@@ -2760,11 +3073,11 @@ extern "C" int b2_get_hidden_f32(b2_engine* e, int32_t layer, int32_t ntokens, f
 
 extern "C" int b2_get_logits(b2_engine* e, int32_t nseq, float* out_logits) {
   B2_REQUIRE(e && out_logits, "b2_get_logits: null argument");
-  B2_REQUIRE(e->cfg.arch == B2_ARCH_LERASUN || ((e->debug_flags & 2) && e->logits), "b2_get_logits: logits capture not enabled (b2_set_debug(e, 2))");
+  B2_REQUIRE(list_arch(e->cfg.arch) || ((e->debug_flags & 2) && e->logits), "b2_get_logits: logits capture not enabled (b2_set_debug(e, 2))");
   B2_REQUIRE(nseq >= 1 && nseq <= e->last_n, "b2_get_logits: nseq %d > sequences of the last forward (%d)", nseq, e->last_n);
   B2_CUDA_OK(cudaSetDevice(e->device));
   const size_t n = (size_t)nseq * e->cfg.vocab;
-  if (e->cfg.arch == B2_ARCH_LERASUN) {  // this family's lm_head writes fp32 rows; the leading rows are the sequences' last positions
+  if (list_arch(e->cfg.arch)) {  // these families' lm_head writes fp32 rows; the leading rows are the sequences' last positions
     B2_CUDA_OK(cudaMemcpyAsync(out_logits, e->l_logits, n * 4, cudaMemcpyDeviceToHost, e->stream));
     B2_CUDA_OK(cudaStreamSynchronize(e->stream));
     return 0;

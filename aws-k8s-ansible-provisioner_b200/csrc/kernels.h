@@ -252,6 +252,47 @@ int launch_unit_norm2(const float* h, const float* gain_a, const float* gain_b, 
 // whose tail is -inf (what the sampler reads; only the first bf16_rows rows)
 int launch_logits_finish(const float* logits, int32_t* out_tokens, bf16* logits_bf16, int bf16_rows, int rows, int V, int v_pad, cudaStream_t s);
 
+// Grouped RMS norm (the vector is cut into `groups` equal pieces, each divided by its own sqrt(mean(piece^2) + eps)) with a plain
+// fp32 gain, around the same fp32 stream:
+int launch_embed_scaled(const int32_t* ids, const void* table, int table_f32, float scale, float* h, int T, int W, int vocab, cudaStream_t s);
+// x[t] = norm(h[rows ? rows[t] : t]) * gain, x fp32 or bf16
+int launch_group_norm(const float* h, const float* gain, void* x, int x_f32, int T, int W, int groups, float eps, const int32_t* rows,
+                      cudaStream_t s);
+// h[t] += norm(y[t] + bias) * gain  (bias may be null): the norm behind a sublayer and the residual add in one pass
+int launch_group_norm_add(float* h, const float* y, const float* bias, const float* gain, int T, int W, int groups, float eps, cudaStream_t s);
+// act[t][i] = g * sigmoid(sharp * g) * (u + 1), g = min(gu[t][i], limit), u = clamp(gu[t][F + i], -limit, limit); gu fp32 [T][2F]
+int launch_clamped_gate(const float* gu, void* act, int act_f32, int T, int F, float limit, float sharp, cudaStream_t s);
+
+// ---- attn_heads.cu: softmax attention with per-head keys and values, any head width, fp32 or bf16 cache ----
+struct HeadsGeom {
+  int heads, kv_heads, dim, vdim;   // query head a reads key/value head a / (heads / kv_heads)
+  int rot_dims;                     // rotary positions on interleaved pairs of the first rot_dims entries of q and k heads (0 = none)
+  float rot_base;
+  float scale, eps;
+  int conv_taps;                    // causal convolution over time on every q / k / v channel (0 = none)
+  int unit_qk;                      // 1: q and k heads are divided by their root mean square
+  int slopes;                       // 1: slope_a * (i - j) is taken off the scores, slope_a = 2^(-slope_exp (a + 1) / heads)
+  float slope_exp;
+  int window, keep_first;           // window > 0: key j is seen from i when i - j < window or j < keep_first
+  int cross;                        // 1: every query head's weights are applied to the values of every key/value head (for talk_gate)
+};
+// proj [T][ld] fp32 = q | k | v (| more) of the fused projection.  bias [heads*dim + kv_heads*(dim+vdim)] or null; conv_w [channels][taps];
+// ring [sequence slots][taps][channels] fp32 (row = position mod taps); row_seq / row_first / row_end [T]: the token's sequence slot and the first row / one past
+// the last row of its portion in this step.  vmix_mode 0 none, 1 the layer supplies v_first [T][kv_heads*vdim], 2 it blends with it by
+// *vmix_lambda.  Writes q_out [T][heads*dim] fp32 and the token's K and V cache rows.
+int launch_heads_finish(const float* proj, int ld, const HeadsGeom& g, const float* bias, const float* conv_w, float* ring,
+                        const int32_t* row_seq, const int32_t* row_first, const int32_t* row_end, const int32_t* positions,
+                        const int32_t* slots, int vmix_mode, const float* vmix_lambda, float* v_first, float* q_out, void* k_cache,
+                        void* v_cache, int cache_f32, int T, cudaStream_t s);
+// tiles == null: decode form (row i is the newest token of block-table row i at positions[i]; seq_lens[i] == 0 rows give zeros).
+// out [T][heads][vdim] (fp32 or bf16), or with g.cross [T][heads][kv_heads*vdim] fp32.
+int launch_heads_attention(const float* q, const void* k_cache, const void* v_cache, int cache_f32, const HeadsGeom& g,
+                           const int32_t* block_table, int bt_stride, int block_size, const PrefillTile* tiles, int ntiles,
+                           const int32_t* positions, const int32_t* seq_lens, void* out, int out_f32, int T, cudaStream_t s);
+// out[t][a][d] = sigmoid(gate[t*gate_ld + a]) * sum_b talk[a][b] * cross[t][b][(a / (heads/kv_heads)) * vdim + d]; gate may be null
+int launch_talk_gate(const float* cross, const float* talk, const float* gate, int gate_ld, void* out, int out_f32, int heads, int kv_heads,
+                     int vdim, int T, cudaStream_t s);
+
 // ---- attn_latent.cu: attention over a shared per-token latent (absorbed form) ----
 // The cache holds, per token, the normalised latent c [kv_rank] and the rotated key piece [rot_dim] side by side
 // (row width kv_rank + rot_dim, element type fp32 or bf16), in pages of block_size tokens.

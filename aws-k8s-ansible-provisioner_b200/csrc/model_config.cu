@@ -8,6 +8,11 @@
 //    "layers": [{"type": "latent_attention",
 //                "mixer": {"heads", "dim", "rot_dim", "vdim", "kv_rank", "scale", "rot": {"base", "dims"}, "kv_from"?},
 //                "mlp": null | {"kind": "moe", "expert": {"ff"}, "router": {"experts", "top", "groups": {"count", "keep"}}}}, ...]}
+// Kedasun by "architecture": "Kedasun":
+//   {"architecture": "Kedasun", "vocab": V, "width": W, "embedding": {"scale": s}, "norm": {"eps": e, "groups": n},
+//    "layers": [{"type": "attention",   "mixer": {"heads", "kv_heads", "dim", "vdim", "scale", "rot": {"base", "dims"}, "v_mix"?}, "mlp": ...},
+//               {"type": "attention_2", "mixer": {"heads", "kv_heads", "dim", "vdim", "scale", "conv", "mask": {"size", "keep_first"}?, "v_mix"?},
+//                "mlp": null | {"kind": "dense", "ff", "limit"}}, ...]}
 #include <fstream>
 #include <sstream>
 #include <string>
@@ -136,6 +141,96 @@ int lerasun_config(const Value& j, b2_config* c, b2_layer_spec* specs, int max_s
   return 0;
 }
 
+int kedasun_config(const Value& j, b2_config* c, b2_layer_spec* specs, int max_specs) {
+  c->arch = B2_ARCH_KEDASUN;
+  CFG_TRY(need_int(j, "vocab", "config", &c->vocab));
+  CFG_TRY(need_int(j, "width", "config", &c->hidden));
+  const Value* norm = j.find("norm");
+  if (!norm || !norm->is_object()) {
+    b2_set_error("config.json: norm missing");
+    return -22;
+  }
+  CFG_TRY(need_float(*norm, "eps", "norm", &c->rms_eps));
+  c->norm_groups = 1;
+  if (const Value* g = norm->find("groups"))
+    if (g->is_number()) c->norm_groups = (int)g->as_int();
+  c->embed_scale = 1.0f;
+  if (const Value* em = j.find("embedding"))
+    if (em->is_object())
+      if (const Value* sc = em->find("scale"))
+        if (sc->is_number()) c->embed_scale = (float)sc->as_double();
+  c->logit_scale = 1.0f;
+  const Value* layers = j.find("layers");
+  if (!layers || !layers->is_array() || layers->size() == 0) {
+    b2_set_error("config.json: layers missing or empty");
+    return -22;
+  }
+  c->num_layers = (int)layers->size();
+  if (c->num_layers > max_specs || specs == nullptr) {
+    b2_set_error("config.json: %d layers, room for %d layer specs", c->num_layers, max_specs);
+    return -22;
+  }
+  for (int i = 0; i < c->num_layers; ++i) {
+    const Value& L = layers->at(i);
+    b2_layer_spec& s = specs[i];
+    memset(&s, 0, sizeof s);
+    s.kv_from = -1;
+    char where[48];
+    snprintf(where, sizeof where, "layers[%d].mixer", i);
+    const Value* type = L.find("type");
+    const Value* m = L.find("mixer");
+    if (!type || !type->is_string() || !m || !m->is_object()) {
+      b2_set_error("config.json: layers[%d] needs type and mixer", i);
+      return -22;
+    }
+    if (type->as_string() == "attention") s.mixer = B2_MIXER_ATTENTION;
+    else if (type->as_string() == "attention_2") s.mixer = B2_MIXER_CONV_ATTENTION;
+    else {
+      b2_set_error("config.json: layers[%d]: mixer type '%s' not built (attention, attention_2)", i, type->as_string().c_str());
+      return -22;
+    }
+    CFG_TRY(need_int(*m, "heads", where, &s.heads));
+    CFG_TRY(need_int(*m, "kv_heads", where, &s.kv_heads));
+    CFG_TRY(need_int(*m, "dim", where, &s.dim));
+    CFG_TRY(need_int(*m, "vdim", where, &s.vdim));
+    CFG_TRY(need_float(*m, "scale", where, &s.scale));
+    if (const Value* vm = m->find("v_mix")) s.v_mix = vm->is_bool() ? (vm->b ? 1 : 0) : (vm->is_number() && vm->as_int() != 0 ? 1 : 0);
+    if (s.mixer == B2_MIXER_ATTENTION) {
+      const Value* rot = m->find("rot");
+      if (rot && rot->is_object()) {  // no "rot": nothing is rotated
+        CFG_TRY(need_float(*rot, "base", where, &s.rot_base));
+        CFG_TRY(need_int(*rot, "dims", where, &s.rot_dims));
+      }
+    } else {
+      CFG_TRY(need_int(*m, "conv", where, &s.conv_taps));
+      const Value* mask = m->find("mask");
+      if (mask && mask->is_object()) {  // no "mask": every earlier key is seen
+        CFG_TRY(need_int(*mask, "size", where, &s.window));
+        if (const Value* kf = mask->find("keep_first"))
+          if (kf->is_number()) s.keep_first = (int)kf->as_int();
+      }
+    }
+    const Value* mlp = L.find("mlp");
+    s.ff = B2_FF_NONE;
+    if (mlp && mlp->is_object()) {
+      snprintf(where, sizeof where, "layers[%d].mlp", i);
+      const Value* kind = mlp->find("kind");
+      if (!kind || !kind->is_string() || kind->as_string() != "dense") {
+        b2_set_error("config.json: %s.kind '%s' not built (dense)", where, kind && kind->is_string() ? kind->as_string().c_str() : "?");
+        return -22;
+      }
+      s.ff = B2_FF_CLAMPED_GATED;
+      CFG_TRY(need_int(*mlp, "ff", where, &s.ff_dim));
+      CFG_TRY(need_float(*mlp, "limit", where, &s.ff_limit));
+    }
+  }
+  c->layer_specs = specs;
+  c->tie_embeddings = 0;
+  c->num_q_heads = c->num_kv_heads = 0;
+  c->head_dim = c->intermediate = 0;
+  return 0;
+}
+
 }  // namespace
 
 extern "C" int b2_config_from_dir(const char* model_dir, b2_config* c, b2_layer_spec* specs, int32_t max_specs) {
@@ -158,9 +253,12 @@ extern "C" int b2_config_from_dir(const char* model_dir, b2_config* c, b2_layer_
   c->abi_version = B2_ABI_VERSION;
   c->layer_specs = nullptr;
   c->logit_scale = 0.f;
+  c->embed_scale = 0.f;
+  c->norm_groups = 0;
   const Value* archv = j.find("architecture");
   if (archv && archv->is_string()) {
     if (archv->as_string() == "Lerasun") return lerasun_config(j, c, specs, max_specs);
+    if (archv->as_string() == "Kedasun") return kedasun_config(j, c, specs, max_specs);
     b2_set_error("%s: architecture '%s' not built", path.c_str(), archv->as_string().c_str());
     return -22;
   }

@@ -108,7 +108,92 @@ __global__ void __launch_bounds__(1024) logits_finish_kernel(const float* __rest
   }
 }
 
+// ---- grouped RMS norm with a plain gain (Kedasun): the vector is `groups` equal pieces, each with its own statistic ----
+template <typename TT>
+__global__ void __launch_bounds__(128) embed_scaled_kernel(const int32_t* __restrict__ ids, const TT* __restrict__ table, float scale,
+                                                           float* __restrict__ h, int W, int vocab) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int t = blockIdx.x;
+  int id = ids[t];
+  id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
+  const TT* row = table + (size_t)id * W;
+  for (int i = threadIdx.x; i < W; i += 128) h[(size_t)t * W + i] = (float)row[i] * scale;
+}
+
+// One CTA per token, one warp per piece (pieces round robin over the four warps).  ADD: h += norm(y + bias) * gain.
+template <typename TX, bool ADD>
+__global__ void __launch_bounds__(128) group_norm_kernel(const float* __restrict__ src, const float* __restrict__ bias,
+                                                         const float* __restrict__ gain, TX* __restrict__ x, float* __restrict__ h, int W,
+                                                         int groups, float eps, const int32_t* __restrict__ rows) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int piece = W / groups;
+  const float* row = src + (size_t)(rows ? rows[t] : t) * W;
+  for (int gi = warp; gi < groups; gi += 4) {
+    const int o = gi * piece;
+    float ss = 0.f;
+    for (int i = lane; i < piece; i += 32) {
+      const float v = row[o + i] + (bias ? bias[o + i] : 0.f);
+      ss = fmaf(v, v, ss);
+    }
+    ss = warp_sum(ss);
+    const float r = 1.0f / sqrtf(ss / (float)piece + eps);
+    for (int i = lane; i < piece; i += 32) {
+      const float v = (row[o + i] + (bias ? bias[o + i] : 0.f)) * r * gain[o + i];
+      if (ADD) h[(size_t)t * W + o + i] += v;
+      else x[(size_t)t * W + o + i] = (TX)v;
+    }
+  }
+}
+
+template <typename TX>
+__global__ void __launch_bounds__(256) clamped_gate_kernel(const float* __restrict__ gu, TX* __restrict__ act, int F, float limit, float sharp) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int t = blockIdx.x;
+  const float* row = gu + (size_t)t * 2 * F;
+  for (int i = threadIdx.x; i < F; i += 256) {
+    const float g = fminf(row[i], limit);
+    const float u = fminf(fmaxf(row[F + i], -limit), limit);
+    act[(size_t)t * F + i] = (TX)(g / (1.0f + expf(-sharp * g)) * (u + 1.0f));
+  }
+}
+
 }  // namespace
+
+int launch_embed_scaled(const int32_t* ids, const void* table, int table_f32, float scale, float* h, int T, int W, int vocab, cudaStream_t s) {
+  if (T <= 0) return 0;
+  if (table_f32) B2_CUDA_OK(b2_launch(embed_scaled_kernel<float>, dim3(T), dim3(128), 0, s, ids, (const float*)table, scale, h, W, vocab));
+  else B2_CUDA_OK(b2_launch(embed_scaled_kernel<bf16>, dim3(T), dim3(128), 0, s, ids, (const bf16*)table, scale, h, W, vocab));
+  return 0;
+}
+
+int launch_group_norm(const float* h, const float* gain, void* x, int x_f32, int T, int W, int groups, float eps, const int32_t* rows,
+                      cudaStream_t s) {
+  if (T <= 0) return 0;
+  B2_REQUIRE(groups >= 1 && W % groups == 0, "group_norm: width %d is not %d equal pieces", W, groups);
+  if (x_f32)
+    B2_CUDA_OK(b2_launch(group_norm_kernel<float, false>, dim3(T), dim3(128), 0, s, h, (const float*)nullptr, gain, (float*)x, (float*)nullptr, W, groups, eps, rows));
+  else
+    B2_CUDA_OK(b2_launch(group_norm_kernel<bf16, false>, dim3(T), dim3(128), 0, s, h, (const float*)nullptr, gain, (bf16*)x, (float*)nullptr, W, groups, eps, rows));
+  return 0;
+}
+
+int launch_group_norm_add(float* h, const float* y, const float* bias, const float* gain, int T, int W, int groups, float eps, cudaStream_t s) {
+  if (T <= 0) return 0;
+  B2_REQUIRE(groups >= 1 && W % groups == 0, "group_norm: width %d is not %d equal pieces", W, groups);
+  B2_CUDA_OK(b2_launch(group_norm_kernel<float, true>, dim3(T), dim3(128), 0, s, y, bias, gain, (float*)nullptr, h, W, groups, eps, (const int32_t*)nullptr));
+  return 0;
+}
+
+int launch_clamped_gate(const float* gu, void* act, int act_f32, int T, int F, float limit, float sharp, cudaStream_t s) {
+  if (T <= 0) return 0;
+  if (act_f32) B2_CUDA_OK(b2_launch(clamped_gate_kernel<float>, dim3(T), dim3(256), 0, s, gu, (float*)act, F, limit, sharp));
+  else B2_CUDA_OK(b2_launch(clamped_gate_kernel<bf16>, dim3(T), dim3(256), 0, s, gu, (bf16*)act, F, limit, sharp));
+  return 0;
+}
 
 int launch_embed_unit_norm(const int32_t* ids, const void* table, int table_f32, const float* gain1p, float* h, int T, int W, int vocab,
                            float eps, cudaStream_t s) {

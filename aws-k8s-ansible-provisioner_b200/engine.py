@@ -41,15 +41,26 @@ class EngineConfig:
     rotary_dim: int = 0          # 0 = head_dim
     max_positions: int = 0       # OPT: learned position table rows - 2 (0 = max_model_len)
     sliding_window: int = 0      # Phi-3: attend to the last N keys only (0 = all)
-    layers: list | None = None   # layer-list families (arch "lerasun"): the "layers" entries of the model's config.json
+    layers: list | None = None   # layer-list families (arch "lerasun", "kedasun"): the "layers" entries of the model's config.json
     compute_f32: bool = False    # families with an fp32 path: operands, weights and cache in fp32
     logit_scale: float = 0.0     # lm_head output multiplier (0 = 1)
+    embed_scale: float = 0.0     # embedding multiplier (0 = 1)
+    norm_groups: int = 0         # Kedasun: pieces of every norm (0 = 1)
 
     @staticmethod
     def lerasun(model_cfg: dict, **runtime) -> "EngineConfig":
         """From the dict a Lerasun config.json holds (width, vocab, norm.eps, logit_scale, layers) plus runtime sizing."""
         return EngineConfig(num_layers=len(model_cfg["layers"]), hidden=model_cfg["width"], vocab=model_cfg["vocab"],
                             rms_eps=model_cfg["norm"]["eps"], logit_scale=model_cfg.get("logit_scale", 1.0), arch="lerasun",
+                            layers=model_cfg["layers"], tie_embeddings=False, num_q_heads=0, num_kv_heads=0, head_dim=0,
+                            intermediate=0, **runtime)
+
+    @staticmethod
+    def kedasun(model_cfg: dict, **runtime) -> "EngineConfig":
+        """From the dict a Kedasun config.json holds (width, vocab, embedding.scale, norm.eps, norm.groups, layers) plus runtime sizing."""
+        return EngineConfig(num_layers=len(model_cfg["layers"]), hidden=model_cfg["width"], vocab=model_cfg["vocab"],
+                            rms_eps=model_cfg["norm"]["eps"], norm_groups=model_cfg["norm"].get("groups", 1),
+                            embed_scale=model_cfg.get("embedding", {}).get("scale", 1.0), logit_scale=1.0, arch="kedasun",
                             layers=model_cfg["layers"], tie_embeddings=False, num_q_heads=0, num_kv_heads=0, head_dim=0,
                             intermediate=0, **runtime)
 
@@ -90,9 +101,12 @@ class Engine:
         c.rms_eps = cfg.rms_eps
         c.rope_theta = cfg.rope_theta
         c.gpu_mem_fraction = cfg.gpu_mem_fraction
-        c.arch = {"qwen3": capi.ARCH_QWEN3, "phi3": capi.ARCH_PHI3, "opt": capi.ARCH_OPT, "lerasun": capi.ARCH_LERASUN}[cfg.arch]
+        c.arch = {"qwen3": capi.ARCH_QWEN3, "phi3": capi.ARCH_PHI3, "opt": capi.ARCH_OPT, "lerasun": capi.ARCH_LERASUN,
+                  "kedasun": capi.ARCH_KEDASUN}[cfg.arch]
         c.compute_f32 = int(cfg.compute_f32)
         c.logit_scale = float(cfg.logit_scale)
+        c.embed_scale = float(cfg.embed_scale)
+        c.norm_groups = int(cfg.norm_groups)
         self._specs = None
         if cfg.layers is not None:
             self._specs = (b2_layer_spec * len(cfg.layers))()
@@ -123,15 +137,17 @@ class Engine:
         c = b2_config()
         specs = (b2_layer_spec * 1024)()
         check(lib.b2_config_from_dir(model_dir.encode(), C.byref(c), specs, 1024), lib)
-        arch = {capi.ARCH_QWEN3: "qwen3", capi.ARCH_PHI3: "phi3", capi.ARCH_OPT: "opt", capi.ARCH_LERASUN: "lerasun"}[c.arch]
+        arch = {capi.ARCH_QWEN3: "qwen3", capi.ARCH_PHI3: "phi3", capi.ARCH_OPT: "opt", capi.ARCH_LERASUN: "lerasun",
+                capi.ARCH_KEDASUN: "kedasun"}[c.arch]
         layers = None
-        if arch == "lerasun":
+        if arch in ("lerasun", "kedasun"):
             layers = [_layer_dict(specs[i]) for i in range(c.num_layers)]
         cfg = EngineConfig(num_layers=c.num_layers, hidden=c.hidden, num_q_heads=c.num_q_heads, num_kv_heads=c.num_kv_heads,
                            head_dim=c.head_dim, intermediate=c.intermediate, vocab=c.vocab, tie_embeddings=bool(c.tie_embeddings),
                            rms_eps=c.rms_eps, rope_theta=c.rope_theta, arch=arch, rotary_dim=c.rotary_dim,
                            max_positions=c.max_positions, sliding_window=c.sliding_window, layers=layers,
-                           compute_f32=(dtype == "float32"), logit_scale=c.logit_scale, **runtime)
+                           compute_f32=(dtype == "float32"), logit_scale=c.logit_scale, embed_scale=c.embed_scale,
+                           norm_groups=c.norm_groups, **runtime)
         return cls(cfg, device=device, safetensors_path=os.path.join(model_dir, "model.safetensors"))
 
     # ---- weights -----------------------------------------------------------------------
@@ -301,7 +317,9 @@ class Engine:
 
 
 def _fill_layer_spec(sp, layer: dict) -> None:
-    """One "layers" entry of a Lerasun config.json -> b2_layer_spec (the C registry does the same for a directory)."""
+    """One "layers" entry of a layer-list config.json -> b2_layer_spec (the C registry does the same for a directory)."""
+    if layer["type"] in ("attention", "attention_2"):
+        return _fill_heads_spec(sp, layer)
     if layer["type"] != "latent_attention":
         raise B2Error("mixer type %r not built" % layer["type"])
     m = layer["mixer"]
@@ -321,7 +339,40 @@ def _fill_layer_spec(sp, layer: dict) -> None:
         sp.groups, sp.groups_keep = int(g["count"]), int(g["keep"])
 
 
+def _fill_heads_spec(sp, layer: dict) -> None:
+    """Kedasun: "attention" (rotary grouped-query attention) and "attention_2" (convolution, window, weight mixing, gate)."""
+    m = layer["mixer"]
+    conv = layer["type"] == "attention_2"
+    sp.mixer = capi.MIXER_CONV_ATTENTION if conv else capi.MIXER_ATTENTION
+    for k in ("heads", "kv_heads", "dim", "vdim"):
+        setattr(sp, k, int(m[k]))
+    sp.scale, sp.kv_from, sp.v_mix = float(m["scale"]), -1, int(bool(m.get("v_mix")))
+    if conv:
+        sp.conv_taps = int(m["conv"])
+        mask = m.get("mask")
+        if mask:
+            sp.window, sp.keep_first = int(mask["size"]), int(mask.get("keep_first", 0))
+    elif m.get("rot"):
+        sp.rot_dims, sp.rot_base = int(m["rot"]["dims"]), float(m["rot"]["base"])
+    mlp = layer.get("mlp")
+    sp.ff = capi.FF_NONE
+    if mlp is not None:
+        if mlp["kind"] != "dense":
+            raise B2Error("feed-forward kind %r not built" % mlp["kind"])
+        sp.ff, sp.ff_dim, sp.ff_limit = capi.FF_CLAMPED_GATED, int(mlp["ff"]), float(mlp["limit"])
+
+
 def _layer_dict(sp) -> dict:
+    if sp.mixer in (capi.MIXER_ATTENTION, capi.MIXER_CONV_ATTENTION):
+        m = {"heads": sp.heads, "kv_heads": sp.kv_heads, "dim": sp.dim, "vdim": sp.vdim, "scale": sp.scale, "v_mix": bool(sp.v_mix)}
+        if sp.mixer == capi.MIXER_CONV_ATTENTION:
+            m["conv"] = sp.conv_taps
+            if sp.window > 0:
+                m["mask"] = {"size": sp.window, "keep_first": sp.keep_first}
+        elif sp.rot_dims > 0:
+            m["rot"] = {"base": sp.rot_base, "dims": sp.rot_dims}
+        mlp = {"kind": "dense", "ff": sp.ff_dim, "limit": sp.ff_limit} if sp.ff == capi.FF_CLAMPED_GATED else None
+        return {"type": "attention_2" if sp.mixer == capi.MIXER_CONV_ATTENTION else "attention", "mixer": m, "mlp": mlp}
     m = {"heads": sp.heads, "dim": sp.dim, "rot_dim": sp.rot_dim, "vdim": sp.vdim, "kv_rank": sp.kv_rank, "scale": sp.scale,
          "rot": {"base": sp.rot_base, "dims": sp.rot_dims}}
     if sp.kv_from >= 0:

@@ -25,15 +25,25 @@
 extern "C" {
 #endif
 
-#define B2_ABI_VERSION 3
+#define B2_ABI_VERSION 4
 
 typedef struct b2_engine b2_engine;
 
 /* One entry of a model whose layers are listed one by one (b2_config.layer_specs): which mixer the layer has, the
  * mixer's sizes and constants, and its feed-forward.  Families whose layers are all alike (Qwen3, Phi-3, OPT) leave
  * the list NULL and describe the layer through the scalar fields of b2_config. */
-enum b2_mixer_kind { B2_MIXER_LATENT_ATTENTION = 1 };
-enum b2_ff_kind { B2_FF_NONE = 0, B2_FF_ROUTED_EXPERTS = 1 };
+enum b2_mixer_kind {
+  B2_MIXER_LATENT_ATTENTION = 1, /* one shared low-rank latent per token (Lerasun) */
+  B2_MIXER_ATTENTION = 2,        /* per-head keys and values, grouped queries, rotary positions on interleaved pairs (Kedasun "attention") */
+  B2_MIXER_CONV_ATTENTION = 3    /* biased projections, a short causal convolution on q / k / v, unit-RMS q and k, a linear distance penalty,
+                                    a window that keeps the first tokens, mixing of the heads' softmax weights, an output gate (Kedasun
+                                    "attention_2") */
+};
+enum b2_ff_kind {
+  B2_FF_NONE = 0,
+  B2_FF_ROUTED_EXPERTS = 1,
+  B2_FF_CLAMPED_GATED = 2        /* y = g sigmoid(1.702 g) (u + 1), g = min(W_g x, limit), u = clamp(W_u x, -limit, limit); out = W_d y */
+};
 typedef struct b2_layer_spec {
   int32_t mixer;        /* b2_mixer_kind */
   int32_t heads;        /* query heads */
@@ -51,6 +61,14 @@ typedef struct b2_layer_spec {
   int32_t top;          /* experts used per token */
   int32_t groups;       /* experts form `groups` equal groups of neighbours ... */
   int32_t groups_keep;  /* ... of which the best groups_keep may supply experts */
+  /* ABI 4: mixers with per-head keys and values (B2_MIXER_ATTENTION, B2_MIXER_CONV_ATTENTION; `dim` is then the whole per-head
+   * query / key width, rot_dim and kv_rank are unused) and the dense feed-forward */
+  int32_t kv_heads;     /* key/value heads; query head a reads key/value head a / (heads / kv_heads) */
+  int32_t conv_taps;    /* taps of the causal convolution over time on every q / k / v channel (0 = none) */
+  int32_t window;       /* > 0: query i sees key j only when i - j < window or j < keep_first (0 = every earlier key) */
+  int32_t keep_first;   /* the first keep_first tokens stay visible whatever the window */
+  int32_t v_mix;        /* 1: the layer takes part in value mixing (the first such layer supplies, the others blend) */
+  float   ff_limit;     /* B2_FF_CLAMPED_GATED: the clamp */
 } b2_layer_spec;
 
 /* Architecture + runtime sizing.  Field meanings follow HF Qwen3Config
@@ -86,6 +104,9 @@ typedef struct b2_config {
   int32_t compute_f32;       /* 1: activations, weights and cache in fp32, every product in true fp32 (families that have such a
                                 path: Lerasun); 0: bf16 operands with fp32 accumulation */
   float   logit_scale;       /* the lm_head's output is multiplied by this (0 = 1) */
+  /* ABI 4 */
+  float   embed_scale;       /* the embedding row is multiplied by this (0 = 1; Kedasun) */
+  int32_t norm_groups;       /* Kedasun: every norm splits its vector into this many equal pieces with a statistic each (0 = 1) */
 } b2_config;
 
 /* Model families.  QWEN3: HF:models/qwen3/modeling_qwen3.py (QK-norm, separate q/k/v and gate/up
@@ -103,11 +124,15 @@ typedef struct b2_config {
  * an earlier layer's cache), feed-forwards are routed squared-ReLU experts.  Tensor names: embed, embed.norm,
  * l<i>.norm1|norm2, l<i>.mix.{q,dkv,dkv.norm,uk,uv,sink,o}, l<i>.mlp.{e<k>.up,e<k>.down,router,correction}, final.norm, head.
  * hidden = width; num_q_heads, head_dim, intermediate are unused. */
-enum b2_arch { B2_ARCH_QWEN3 = 0, B2_ARCH_PHI3 = 1, B2_ARCH_OPT = 2, B2_ARCH_LERASUN = 3 };
+/* KEDASUN: a layer list as well.  h <- h + n1b(mixer(n1(h))), then h <- h + n2b(ff(n2(h))) on an fp32 residual stream; every norm
+ * is an RMS norm over norm_groups pieces with a plain gain; the embedding is scaled by embed_scale.  Mixers: B2_MIXER_ATTENTION and
+ * B2_MIXER_CONV_ATTENTION; feed-forward: B2_FF_CLAMPED_GATED or none.  Tensor names: embed, l<i>.norm1|norm1b|norm2|norm2b,
+ * l<i>.mix.{q,k,v,o,vmix} (+ .b biases, {q,k,v}.conv, talk, g for the convolution mixer), l<i>.mlp.{gate,up,down}, final.norm, head. */
+enum b2_arch { B2_ARCH_QWEN3 = 0, B2_ARCH_PHI3 = 1, B2_ARCH_OPT = 2, B2_ARCH_LERASUN = 3, B2_ARCH_KEDASUN = 4 };
 
 /* Model registry: reads MODEL_DIR/config.json and fills the architecture fields of *cfg (the runtime sizing fields --
  * max_model_len, block_size, num_blocks, max_seqs, max_batch_tokens, use_cuda_graphs, compute_f32 -- are left as the caller
- * set them).  HF configs are told apart by "model_type" (qwen3, phi3, opt); a config with "architecture": "Lerasun" fills
+ * set them).  HF configs are told apart by "model_type" (qwen3, phi3, opt); a config with "architecture": "Lerasun" or "Kedasun" fills
  * specs[0 .. num_layers) as well and points cfg->layer_specs at it (max_specs = capacity of specs; may be 0 / NULL for the
  * HF families).  Returns 0, or a negative code with b2_last_error(). */
 int  b2_config_from_dir(const char* model_dir, b2_config* cfg, b2_layer_spec* specs, int32_t max_specs);
