@@ -1680,7 +1680,7 @@ int heads_engine_alloc(b2_engine* e) {
     L.nqd = L.nq + L.nk + L.nv + (conv ? sp.heads : 0);
     if (sp.v_mix) {
       if (first_vmix < 0) first_vmix = l;
-      B2_REQUIRE(e->ll[first_vmix].nv == L.nv, "layer %d: value mixing needs the value sizes of layer %d", l, first_vmix);
+      B2_REQUIRE(e->specs[first_vmix].kv_heads == sp.kv_heads && e->specs[first_vmix].vdim == sp.vdim, "layer %d: value mixing needs the value sizes of layer %d", l, first_vmix);
       L.vmix_mode = first_vmix == l ? 1 : 2;
     }
     B2_TRY(xalloc(&L.wqd, (size_t)L.nqd * W));

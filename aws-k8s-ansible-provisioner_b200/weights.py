@@ -108,3 +108,46 @@ def lerasun_random_state_dict(model_cfg: dict, seed: int = 0) -> dict[str, torch
             t = torch.randn(shape, generator=g) * (shape[-1] ** -0.5)
         sd[name] = t.to(torch.bfloat16)
     return sd
+
+
+def kedasun_tensor_shapes(model_cfg: dict) -> dict[str, tuple[int, ...]]:
+    """Tensor names and shapes of a Kedasun checkpoint for the dict its config.json holds."""
+    W, V = model_cfg["width"], model_cfg["vocab"]
+    s: dict[str, tuple[int, ...]] = {"embed": (V, W)}
+    for i, layer in enumerate(model_cfg["layers"]):
+        m, mlp, p = layer["mixer"], layer.get("mlp"), f"l{i}."
+        H, G, D, Dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+        s[p + "norm1"], s[p + "norm1b"] = (W,), (W,)
+        s[p + "mix.q"], s[p + "mix.k"], s[p + "mix.v"] = (H * D, W), (G * D, W), (G * Dv, W)
+        s[p + "mix.vmix"], s[p + "mix.o"] = (), (W, H * Dv)
+        if layer["type"] == "attention_2":
+            for n, c in (("q", H * D), ("k", G * D), ("v", G * Dv)):
+                s[p + f"mix.{n}.b"], s[p + f"mix.{n}.conv"] = (c,), (c, m["conv"])
+            s[p + "mix.talk"], s[p + "mix.g"], s[p + "mix.o.b"] = (H, H), (H, W), (W,)
+        if mlp is not None:
+            s[p + "norm2"], s[p + "norm2b"] = (W,), (W,)
+            s[p + "mlp.gate"], s[p + "mlp.up"], s[p + "mlp.down"] = (mlp["ff"], W), (mlp["ff"], W), (W, mlp["ff"])
+    s["final.norm"] = (W,)
+    s["head"] = (V, W)
+    return s
+
+
+def kedasun_random_state_dict(model_cfg: dict, seed: int = 0) -> dict[str, torch.Tensor]:
+    """Random bf16 weights scaled by 1/sqrt(fan-in), gains around one, a near-identity weight-mixing matrix."""
+    g = torch.Generator().manual_seed(seed)
+    sd = {}
+    for name, shape in kedasun_tensor_shapes(model_cfg).items():
+        if "norm" in name:
+            t = 1.0 + 0.1 * torch.randn(shape, generator=g)
+        elif name.endswith("vmix"):
+            t = torch.rand(shape, generator=g)
+        elif name.endswith("talk"):
+            t = torch.eye(shape[0]) + 0.2 * torch.randn(shape, generator=g)
+        elif name.endswith(".b"):
+            t = 0.1 * torch.randn(shape, generator=g)
+        elif name == "embed":
+            t = 0.5 * torch.randn(shape, generator=g)
+        else:
+            t = torch.randn(shape, generator=g) * (shape[-1] ** -0.5)
+        sd[name] = t.to(torch.bfloat16)
+    return sd

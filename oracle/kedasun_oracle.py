@@ -34,8 +34,6 @@ last projected values the convolutions need), so that the two can be compared.
 """
 from __future__ import annotations
 
-import math
-
 import torch
 
 GATE_SHARPNESS = 1.702      # y = g * sigmoid(GATE_SHARPNESS * g) * (u + 1)
@@ -151,7 +149,7 @@ class Stepper:
         self.first = first_value_layer(cfg)
 
     def _norm(self, x, name):
-        return grouped_rms_norm(x, self.w[name], self.cfg["norm"]["groups"], self.cfg["norm"]["eps"])
+        return grouped_rms_norm(x, self.w[name], self.cfg["norm"].get("groups", 1), self.cfg["norm"]["eps"])
 
     def _mixer(self, li, L, x, pos, v_first):
         m, w, pre = L["mixer"], self.w, "l%d.mix." % li
@@ -174,7 +172,7 @@ class Stepper:
         q, k, v = q.reshape(T, H, D), k.reshape(T, G, D), v.reshape(T, G, Dv)
         if two:
             q, k = unit_rms(q, self.cfg["norm"]["eps"]), unit_rms(k, self.cfg["norm"]["eps"])
-        else:
+        elif m.get("rot"):
             q = rotate_pairs(q, pos, m["rot"]["base"], m["rot"]["dims"])
             k = rotate_pairs(k, pos, m["rot"]["base"], m["rot"]["dims"])
         if m.get("v_mix"):
@@ -186,8 +184,9 @@ class Stepper:
         self.vals[li] = v if self.vals[li] is None else torch.cat([self.vals[li], v], 0)
         kpos = torch.arange(self.keys[li].shape[0])
         if two:
+            mask = m.get("mask")
             o = attend(q, self.keys[li], self.vals[li], pos, kpos, m["scale"], slopes=head_slopes(H, self.dtype),
-                       window=m["mask"]["size"], keep_first=m["mask"]["keep_first"], talk=w[pre + "talk"])
+                       window=mask["size"] if mask else None, keep_first=mask.get("keep_first", 0) if mask else 0, talk=w[pre + "talk"])
             o = o * torch.sigmoid(x @ w[pre + "g"].T)[:, :, None]
             return o.reshape(T, H * Dv) @ w[pre + "o"].T + w[pre + "o.b"], v_first
         o = attend(q, self.keys[li], self.vals[li], pos, kpos, m["scale"])
@@ -197,7 +196,7 @@ class Stepper:
         cfg, w = self.cfg, self.w
         tok = torch.as_tensor(tokens, dtype=torch.long)
         pos = torch.arange(self.n, self.n + len(tok))
-        h = w["embed"][tok] * cfg["embedding"]["scale"]
+        h = w["embed"][tok] * cfg.get("embedding", {}).get("scale", 1.0)
         streams = [h.clone()]
         v_first = None
         for li, L in enumerate(cfg["layers"]):
@@ -210,6 +209,16 @@ class Stepper:
             streams.append(h.clone())
         self.n += len(tok)
         return self._norm(h, "final.norm") @ w["head"].T, streams
+
+
+    def greedy(self, prompt, steps: int):
+        out = []
+        logits, _ = self.feed(prompt)
+        for _ in range(steps):
+            t = int(logits[-1].argmax())
+            out.append(t)
+            logits, _ = self.feed([t])
+        return out
 
 
 def forward(cfg: dict, w: dict, tokens, dtype=torch.float64):
@@ -225,12 +234,15 @@ def random_weights(cfg: dict, seed: int, spread: float = 1.0) -> dict:
     def r(*shape, s=1.0):
         return (torch.randn(*shape, generator=g) * s * spread).to(torch.bfloat16).to(torch.float32)
 
-    w = {"embed": r(cfg["vocab"], W, s=0.5), "head": r(cfg["vocab"], W, s=W ** -0.5), "final.norm": 1.0 + r(W, s=0.1)}
+    def gain():
+        return (1.0 + r(W, s=0.1)).to(torch.bfloat16).to(torch.float32)
+
+    w = {"embed": r(cfg["vocab"], W, s=0.5), "head": r(cfg["vocab"], W, s=W ** -0.5), "final.norm": gain()}
     for i, L in enumerate(cfg["layers"]):
         m, p = L["mixer"], "l%d." % i
         H, G, D, Dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
         for n in ("norm1", "norm1b") + (("norm2", "norm2b") if L.get("mlp") else ()):
-            w[p + n] = 1.0 + r(W, s=0.1)
+            w[p + n] = gain()
         w[p + "mix.q"], w[p + "mix.k"] = r(H * D, W, s=W ** -0.5), r(G * D, W, s=W ** -0.5)
         w[p + "mix.v"], w[p + "mix.o"] = r(G * Dv, W, s=W ** -0.5), r(W, H * Dv, s=(H * Dv) ** -0.5)
         w[p + "mix.vmix"] = torch.rand((), generator=g).to(torch.bfloat16).to(torch.float32)
