@@ -27,6 +27,8 @@
 //                     With weight mixing ("cross") a query head's weights are applied to the values of EVERY key/value head
 //                     (out [heads][kv_heads * vdim], normalised per head), because the mixed output of head a is
 //                     sum_b talk[a][b] * (weights of head b applied to the values of a's key/value head)
+//   heads_attention_mma   bf16 caches and prompt portions, head sizes in multiples of 16 / 8: the same pass on warp-level tensor-core
+//                     MMAs, 64 query tokens of one head per CTA (see at the kernel)
 //   talk_gate         that sum, times the gate, rounded to the operand type
 #include "kernels.h"
 
@@ -311,6 +313,212 @@ __global__ void __launch_bounds__(128) talk_gate_kernel(const float* __restrict_
   }
 }
 
+
+// ---- bf16 caches, prompt portions: 64 query tokens of one head per CTA on warp-level tensor-core MMAs ----
+// Four warps of 16 query rows; key tiles of 64 in shared memory.  S = Q.K^T (m16n8k16, fp32 accumulators), the scale, the
+// distance penalty and the mask in fp32 on the accumulator fragments, online softmax with the row statistics in registers, P rounded
+// to bf16 as the A operand of O += P.V (V fragments through ldmatrix.trans), row sums from the unrounded weights.  Key tiles
+// run from position 0 upwards whatever the batch holds, and tiles that no row of the CTA can see (between the kept first
+// tokens and the window) are skipped.  cross: blockIdx.z names the key/value head whose values the weights are applied to.
+// KD = dim / 16, NO = vdim / 8.
+constexpr int HM_ROWS = 64, HM_KEYS = 64, HM_PAD = 8;
+
+__device__ __forceinline__ void mma_bf16_16816(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t* r, uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+
+template <int KD, int NO, typename TO>
+__global__ void __launch_bounds__(128) heads_attention_mma_kernel(const float* __restrict__ q, const bf16* __restrict__ k_cache,
+                                                                  const bf16* __restrict__ v_cache, HeadsGeom g,
+                                                                  const int32_t* __restrict__ block_table, int bt_stride, int block_size,
+                                                                  const PrefillTile* __restrict__ tiles, TO* __restrict__ out) {
+  constexpr int D = KD * 16, DV = NO * 8, QS = D + HM_PAD, VS = DV + HM_PAD;
+  extern __shared__ __align__(16) unsigned char smraw[];
+  bf16* Qs = reinterpret_cast<bf16*>(smraw);       // [64][QS]
+  bf16* Ks = Qs + HM_ROWS * QS;                    // [64][QS]
+  bf16* Vs = Ks + HM_KEYS * QS;                    // [64][VS]
+  pdl_wait();
+  pdl_launch_dependents();
+  const PrefillTile tl = tiles[blockIdx.x];
+  if (tl.nrows <= 0) return;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gq = lane >> 2, tq = lane & 3;
+  const int a = blockIdx.y, kvh = a / (g.heads / g.kv_heads), vh = g.cross ? (int)blockIdx.z : kvh;
+  const int krow = g.kv_heads * D, vrow = g.kv_heads * DV;
+  // queries: fp32 -> bf16, rows past the tile's end are zero
+  for (int i = threadIdx.x; i < HM_ROWS * (D / 4); i += 128) {
+    const int r = i / (D / 4), c4 = (i - r * (D / 4)) * 4;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (r < tl.nrows) v = *reinterpret_cast<const float4*>(q + ((size_t)(tl.q_row0 + r) * g.heads + a) * D + c4);
+    uint2 pk;
+    pk.x = pack_bf16x2(v.x, v.y);
+    pk.y = pack_bf16x2(v.z, v.w);
+    *reinterpret_cast<uint2*>(Qs + r * QS + c4) = pk;
+  }
+  __syncthreads();
+  uint32_t qa[KD][4];
+  {
+    const bf16* q0 = Qs + (warp * 16 + gq) * QS + 2 * tq;
+#pragma unroll
+    for (int kk = 0; kk < KD; ++kk) {
+      qa[kk][0] = *reinterpret_cast<const uint32_t*>(q0 + kk * 16);
+      qa[kk][1] = *reinterpret_cast<const uint32_t*>(q0 + 8 * QS + kk * 16);
+      qa[kk][2] = *reinterpret_cast<const uint32_t*>(q0 + kk * 16 + 8);
+      qa[kk][3] = *reinterpret_cast<const uint32_t*>(q0 + 8 * QS + kk * 16 + 8);
+    }
+  }
+  const float slope = g.slopes ? (float)exp2(-(double)g.slope_exp * (double)(a + 1) / (double)g.heads) : 0.f;
+  const int r0 = warp * 16 + gq, r1 = r0 + 8;                 // this thread's two query rows
+  const int p0 = tl.q_pos0 + r0, p1 = tl.q_pos0 + r1;
+  const bool live0 = r0 < tl.nrows, live1 = r1 < tl.nrows;
+  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+  float o[NO][4];
+#pragma unroll
+  for (int n = 0; n < NO; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+  // key tiles some row of the CTA sees
+  const int last_key = tl.q_pos0 + tl.nrows - 1, last_tile = last_key / HM_KEYS;
+  int nA = 0, tB = 0;
+  if (g.window > 0) {
+    const int lo_min = max(tl.q_pos0 - g.window + 1, 0);
+    nA = (min(g.keep_first, lo_min) + HM_KEYS - 1) / HM_KEYS;
+    tB = max(lo_min / HM_KEYS, nA);
+  }
+  const int total = nA + (last_tile - tB + 1);
+  const int32_t* bt = block_table + (size_t)tl.bt_row * bt_stride;
+  constexpr float LOG2E = 1.4426950408889634f;
+  for (int vi = 0; vi < total; ++vi) {
+    const int key0 = (vi < nA ? vi : tB + (vi - nA)) * HM_KEYS;
+    __syncthreads();  // the previous tile's fragments are read
+    for (int i = threadIdx.x; i < HM_KEYS * (D / 8); i += 128) {
+      const int r = i / (D / 8), c8 = (i - r * (D / 8)) * 8, j = key0 + r;
+      uint4 v = make_uint4(0u, 0u, 0u, 0u);
+      if (j <= last_key) v = *reinterpret_cast<const uint4*>(k_cache + ((size_t)bt[j / block_size] * block_size + j % block_size) * krow + (size_t)kvh * D + c8);
+      *reinterpret_cast<uint4*>(Ks + r * QS + c8) = v;
+    }
+    for (int i = threadIdx.x; i < HM_KEYS * (DV / 8); i += 128) {
+      const int r = i / (DV / 8), c8 = (i - r * (DV / 8)) * 8, j = key0 + r;
+      uint4 v = make_uint4(0u, 0u, 0u, 0u);
+      if (j <= last_key) v = *reinterpret_cast<const uint4*>(v_cache + ((size_t)bt[j / block_size] * block_size + j % block_size) * vrow + (size_t)vh * DV + c8);
+      *reinterpret_cast<uint4*>(Vs + r * VS + c8) = v;
+    }
+    __syncthreads();
+    float sc[HM_KEYS / 8][4];
+#pragma unroll
+    for (int n = 0; n < HM_KEYS / 8; ++n) {
+      sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.f;
+      const bf16* kb = Ks + (n * 8 + gq) * QS + 2 * tq;
+#pragma unroll
+      for (int kk = 0; kk < KD; ++kk)
+        mma_bf16_16816(sc[n], qa[kk], *reinterpret_cast<const uint32_t*>(kb + kk * 16), *reinterpret_cast<const uint32_t*>(kb + kk * 16 + 8));
+    }
+    // scale, distance penalty, mask; row maxima over the quad
+    float t0 = -INFINITY, t1 = -INFINITY;
+#pragma unroll
+    for (int n = 0; n < HM_KEYS / 8; ++n) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int j = key0 + n * 8 + 2 * tq + (e & 1);
+        const int p = (e & 2) ? p1 : p0;
+        const bool ok = ((e & 2) ? live1 : live0) && j <= p && (g.window <= 0 || p - j < g.window || j < g.keep_first);
+        const float v = ok ? sc[n][e] * g.scale - slope * (float)(p - j) : -INFINITY;
+        sc[n][e] = v;
+        if (e & 2) t1 = fmaxf(t1, v);
+        else t0 = fmaxf(t0, v);
+      }
+    }
+    t0 = fmaxf(t0, __shfl_xor_sync(0xffffffffu, t0, 1));
+    t0 = fmaxf(t0, __shfl_xor_sync(0xffffffffu, t0, 2));
+    t1 = fmaxf(t1, __shfl_xor_sync(0xffffffffu, t1, 1));
+    t1 = fmaxf(t1, __shfl_xor_sync(0xffffffffu, t1, 2));
+    const float n0 = fmaxf(m0, t0), n1 = fmaxf(m1, t1);
+    const float u0 = n0 == -INFINITY ? 0.f : n0, u1 = n1 == -INFINITY ? 0.f : n1;   // a row that has seen no key yet
+    const float c0 = exp2f((m0 - u0) * LOG2E), c1 = exp2f((m1 - u1) * LOG2E);
+    m0 = n0;
+    m1 = n1;
+    float s0 = 0.f, s1 = 0.f;
+    uint32_t pa[HM_KEYS / 16][4];
+#pragma unroll
+    for (int n = 0; n < HM_KEYS / 8; ++n) {
+      const float e0 = exp2f((sc[n][0] - u0) * LOG2E), e1 = exp2f((sc[n][1] - u0) * LOG2E);
+      const float e2 = exp2f((sc[n][2] - u1) * LOG2E), e3 = exp2f((sc[n][3] - u1) * LOG2E);
+      s0 += e0 + e1;
+      s1 += e2 + e3;
+      pa[n >> 1][(n & 1) * 2] = pack_bf16x2(e0, e1);
+      pa[n >> 1][(n & 1) * 2 + 1] = pack_bf16x2(e2, e3);
+    }
+    l0 = l0 * c0 + s0;
+    l1 = l1 * c1 + s1;
+#pragma unroll
+    for (int n = 0; n < NO; ++n) {
+      o[n][0] *= c0; o[n][1] *= c0;
+      o[n][2] *= c1; o[n][3] *= c1;
+    }
+#pragma unroll
+    for (int kk = 0; kk < HM_KEYS / 16; ++kk) {
+      const uint32_t vbase = smem_u32(Vs + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * VS + (lane >> 4) * 8);
+#pragma unroll
+      for (int n = 0; n < NO; n += 2) {
+        uint32_t vb[4];
+        ldmatrix_x4_trans(vb, vbase + n * 8 * 2);
+        mma_bf16_16816(o[n], pa[kk], vb[0], vb[1]);
+        mma_bf16_16816(o[n + 1], pa[kk], vb[2], vb[3]);
+      }
+    }
+  }
+  // row sums over the quad, then the output
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+  const int ow = g.cross ? vrow : DV, ooff = g.cross ? vh * DV : 0;
+  if (live0) {
+    const float inv = 1.0f / l0;
+    TO* orow = out + ((size_t)(tl.q_row0 + r0) * g.heads + a) * ow + ooff + 2 * tq;
+#pragma unroll
+    for (int n = 0; n < NO; ++n) {
+      stf(orow + n * 8, o[n][0] * inv);
+      stf(orow + n * 8 + 1, o[n][1] * inv);
+    }
+  }
+  if (live1) {
+    const float inv = 1.0f / l1;
+    TO* orow = out + ((size_t)(tl.q_row0 + r1) * g.heads + a) * ow + ooff + 2 * tq;
+#pragma unroll
+    for (int n = 0; n < NO; ++n) {
+      stf(orow + n * 8, o[n][2] * inv);
+      stf(orow + n * 8 + 1, o[n][3] * inv);
+    }
+  }
+}
+
+template <int KD, int NO, typename TO>
+int launch_attention_mma_t(const float* q, const bf16* k, const bf16* v, const HeadsGeom& g, const int32_t* bt, int bt_stride, int block_size,
+                           const PrefillTile* tiles, int ntiles, TO* out, cudaStream_t s) {
+  const size_t smem = ((size_t)2 * HM_ROWS * (KD * 16 + HM_PAD) + (size_t)HM_KEYS * (NO * 8 + HM_PAD)) * sizeof(bf16);
+  auto kern = heads_attention_mma_kernel<KD, NO, TO>;
+  if (smem > 48 * 1024) B2_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  B2_CUDA_OK(b2_launch(kern, dim3(ntiles, g.heads, g.cross ? g.kv_heads : 1), dim3(128), smem, s, q, k, v, g, bt, bt_stride, block_size, tiles, out));
+  return 0;
+}
+
+// 1 = launched; 0 = the sizes have no tensor-core form (the caller takes the plain kernel)
+template <typename TO>
+int launch_attention_mma(const float* q, const bf16* k, const bf16* v, const HeadsGeom& g, const int32_t* bt, int bt_stride, int block_size,
+                         const PrefillTile* tiles, int ntiles, TO* out, cudaStream_t s, int* rc) {
+#define HM_CASE(DD, VV)                                                                                                            \
+  if (g.dim == DD && g.vdim == VV) {                                                                                               \
+    *rc = launch_attention_mma_t<DD / 16, VV / 8, TO>(q, k, v, g, bt, bt_stride, block_size, tiles, ntiles, out, s);                 \
+    return 1;                                                                                                                      \
+  }
+  HM_CASE(32, 32) HM_CASE(64, 32) HM_CASE(64, 64) HM_CASE(96, 64) HM_CASE(96, 96) HM_CASE(128, 64) HM_CASE(128, 128) HM_CASE(192, 128) HM_CASE(256, 128)
+#undef HM_CASE
+  return 0;
+}
+
 template <typename TC, typename TO, bool DECODE>
 int launch_attention_nv(int nv, dim3 grid, size_t smem, cudaStream_t s, const float* q, const TC* k, const TC* v, const HeadsGeom& g,
                         const int32_t* bt, int bt_stride, int block_size, const PrefillTile* tiles, const int32_t* positions,
@@ -383,6 +591,13 @@ int launch_heads_attention(const float* q, const void* k_cache, const void* v_ca
   if (cache_f32) {
     B2_REQUIRE(out_f32, "heads_attention: an fp32 cache goes with fp32 operands");
     return launch_attention_t<float, float>(q, k_cache, v_cache, g, block_table, bt_stride, block_size, tiles, ntiles, positions, seq_lens, out, T, s);
+  }
+  static const bool use_mma = [] { const char* e = getenv("B2_HEADS_MMA"); return !(e && *e == '0'); }();
+  if (use_mma && tiles != nullptr && block_size > 0) {   // prompt portions on tensor-core MMAs when the head sizes have that form
+    int rc = 0;
+    if (out_f32 ? launch_attention_mma<float>(q, (const bf16*)k_cache, (const bf16*)v_cache, g, block_table, bt_stride, block_size, tiles, ntiles, (float*)out, s, &rc)
+                : launch_attention_mma<bf16>(q, (const bf16*)k_cache, (const bf16*)v_cache, g, block_table, bt_stride, block_size, tiles, ntiles, (bf16*)out, s, &rc))
+      return rc;
   }
   if (out_f32)
     return launch_attention_t<bf16, float>(q, k_cache, v_cache, g, block_table, bt_stride, block_size, tiles, ntiles, positions, seq_lens, out, T, s);

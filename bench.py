@@ -449,9 +449,37 @@ def lerasun_model_cfg(width, heads, rank, experts, top, ff, groups, keep, layers
     return {"architecture": "Lerasun", "vocab": vocab, "width": width, "logit_scale": 1.0, "norm": {"eps": 1e-6}, "layers": ls}
 
 
+# ---- --family kedasun: width, heads, kv heads, feed-forward width (heads 128 wide, 4 layers of which one is the convolution / window mixer, vocab 32000)
+KEDASUN_SIZES = {"w1024": (1024, 8, 4, 3072), "w2048": (2048, 16, 8, 6144), "w4096": (4096, 32, 16, 11008)}
+
+
+def kedasun_model_cfg(width, heads, kv, ff, layers=4, vocab=32000):
+    rot = {"heads": heads, "kv_heads": kv, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "rot": {"base": 10000.0, "dims": 64}, "v_mix": True}
+    win = {"heads": heads, "kv_heads": kv, "dim": 128, "vdim": 128, "scale": 1.0, "conv": 4, "mask": {"size": 512, "keep_first": 16}, "v_mix": True}
+    mlp = {"kind": "dense", "ff": ff, "limit": 7.0}
+    ls = [{"type": "attention_2", "mixer": win, "mlp": mlp} if i % 4 == 2 else {"type": "attention", "mixer": rot, "mlp": mlp} for i in range(layers)]
+    return {"architecture": "Kedasun", "vocab": vocab, "width": width, "embedding": {"scale": 1.0}, "norm": {"eps": 1e-6, "groups": 4}, "layers": ls}
+
+
+def family_models(pkg, weights, family, tag):
+    """(name, engine configuration, state-dict maker) of the family's model and of Qwen3 at the same width, depth, heads and feed-forward size."""
+    if family == "kedasun":
+        width, heads, kv, ff = KEDASUN_SIZES[tag]
+        mc = kedasun_model_cfg(width, heads, kv, ff)
+        return [("kedasun", pkg.EngineConfig.kedasun(mc), lambda c: weights.kedasun_random_state_dict(mc, seed=0)),
+                ("qwen3", pkg.EngineConfig(num_layers=4, hidden=width, num_q_heads=heads, num_kv_heads=kv, head_dim=128, intermediate=ff, vocab=32000),
+                 lambda c: weights.random_state_dict(c, seed=0))]
+    width, heads, rank, experts, top, ff, groups, keep = FAMILY_SIZES[tag]
+    mc = lerasun_model_cfg(width, heads, rank, experts, top, ff, groups, keep)
+    inter = ((2 * top * ff // 3) + 255) // 256 * 256      # SwiGLU with the same active feed-forward parameters
+    return [("lerasun", pkg.EngineConfig.lerasun(mc), lambda c: weights.lerasun_random_state_dict(mc, seed=0)),
+            ("qwen3", pkg.EngineConfig(num_layers=4, hidden=width, num_q_heads=heads, num_kv_heads=heads // 2, head_dim=128,
+                                       intermediate=inter, vocab=32000), lambda c: weights.random_state_dict(c, seed=0))]
+
+
 def run_family(args, local):
-    """Prefill and decode throughput of Lerasun at layer sizes of real models (random weights), and of Qwen3 at the same
-    width, depth, head count and active feed-forward size: one JSON line per size and model, with the decode step's
+    """Prefill and decode throughput of a layer-list family (Lerasun, Kedasun) at layer sizes of real models (random weights), and of
+    Qwen3 at the same width, depth, head count and (active) feed-forward size: one JSON line per size and model, with the decode step's
     per-kernel-class times (CUDA events around every launch of an eager step)."""
     import torch
 
@@ -460,12 +488,9 @@ def run_family(args, local):
     B, PL, NEW = args.family_batch, args.family_prompt, 72
     peaks = measured_peaks()
     for tag in args.family_sizes.split(","):
-        width, heads, rank, experts, top, ff, groups, keep = FAMILY_SIZES[tag]
-        mc = lerasun_model_cfg(width, heads, rank, experts, top, ff, groups, keep)
-        inter = ((2 * top * ff // 3) + 255) // 256 * 256      # SwiGLU with the same active feed-forward parameters
-        models = [("lerasun", pkg.EngineConfig.lerasun(mc), lambda c: weights.lerasun_random_state_dict(mc, seed=0)),
-                  ("qwen3", pkg.EngineConfig(num_layers=4, hidden=width, num_q_heads=heads, num_kv_heads=heads // 2, head_dim=128,
-                                             intermediate=inter, vocab=32000), lambda c: weights.random_state_dict(c, seed=0))]
+        models = family_models(pkg, weights, args.family, tag)
+        if args.family_only:
+            models = [m for m in models if m[0] == args.family_only]
         for name, cfg, make_sd in models:
             cfg.max_model_len, cfg.max_seqs, cfg.max_batch_tokens, cfg.use_cuda_graphs = PL + NEW + 16, B, B * PL, True
             cfg.num_blocks = B * ((cfg.max_model_len + 15) // 16) + 8
@@ -508,9 +533,10 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--value-only", action="store_true", help="device-resident timing only (ablation runs)")
-    ap.add_argument("--family", default="", choices=["", "lerasun"],
+    ap.add_argument("--family", default="", choices=["", "lerasun", "kedasun"],
                     help="instead of the headline workload: the named family beside the closest GQA model at equal size (one GPU)")
     ap.add_argument("--family-sizes", default="w1024,w2048,w4096")
+    ap.add_argument("--family-only", default="", help="time only the named model of the pair (the family's name, or qwen3)")
     ap.add_argument("--family-batch", type=int, default=16)
     ap.add_argument("--family-prompt", type=int, default=1024)
     args = ap.parse_args()
