@@ -169,7 +169,12 @@ __device__ __forceinline__ TileRange visible_tiles(int i, int window, int keep_f
 
 // NV = ceil(value columns / 32).  DECODE: a CTA is one (sequence, head), its warps take the visible key tiles round robin;
 // else a CTA is eight query tokens of one tile and one head, a warp per token.
-template <typename TC, typename TO, int NV, bool DECODE>
+// VEC (bf16 caches, dim a multiple of 8, value columns a multiple of 64): a lane reads its key's row 16 bytes at a time and owns
+// value columns in pairs (64 n + 2 lane, + 1), one 4-byte load per pair; otherwise element by element, columns lane + 32 n.
+template <bool VEC>
+__device__ __forceinline__ int ha_col(int n, int lane) { return VEC ? 64 * (n >> 1) + 2 * lane + (n & 1) : lane + 32 * n; }
+
+template <typename TC, typename TO, int NV, bool DECODE, bool VEC>
 __global__ void __launch_bounds__(HA_WARPS * 32) heads_attention_kernel(const float* __restrict__ q, const TC* __restrict__ k_cache,
                                                                         const TC* __restrict__ v_cache, HeadsGeom g,
                                                                         const int32_t* __restrict__ block_table, int bt_stride, int block_size,
@@ -227,7 +232,19 @@ __global__ void __launch_bounds__(HA_WARPS * 32) heads_attention_kernel(const fl
         slot = (size_t)bt[j / block_size] * block_size + j % block_size;
         const TC* kr = k_cache + slot * krow + (size_t)kvh * D;
         float dot = 0.f;
-        for (int d = 0; d < D; ++d) dot = fmaf(qs[d], ldf(kr + d), dot);
+        if (VEC) {
+          const uint4* kp = reinterpret_cast<const uint4*>(kr);
+          for (int d8 = 0; d8 < D / 8; ++d8) {
+            const uint4 u = kp[d8];
+            const float4 qa = *reinterpret_cast<const float4*>(qs + 8 * d8), qb = *reinterpret_cast<const float4*>(qs + 8 * d8 + 4);
+            dot = fmaf(qa.x, bf16lo(u.x), dot); dot = fmaf(qa.y, bf16hi(u.x), dot);
+            dot = fmaf(qa.z, bf16lo(u.y), dot); dot = fmaf(qa.w, bf16hi(u.y), dot);
+            dot = fmaf(qb.x, bf16lo(u.z), dot); dot = fmaf(qb.y, bf16hi(u.z), dot);
+            dot = fmaf(qb.z, bf16lo(u.w), dot); dot = fmaf(qb.w, bf16hi(u.w), dot);
+          }
+        } else {
+          for (int d = 0; d < D; ++d) dot = fmaf(qs[d], ldf(kr + d), dot);
+        }
         s = dot * g.scale - slope * (float)(pos - j);
       }
       const float mt = warp_max(s);  // finite: a visited tile holds at least one visible key
@@ -245,10 +262,19 @@ __global__ void __launch_bounds__(HA_WARPS * 32) heads_attention_kernel(const fl
         const float pj = __shfl_sync(0xffffffffu, p, jj);
         const size_t sj = __shfl_sync(0xffffffffu, (unsigned long long)slot, jj);
         const TC* vr = v_cache + sj * vrow + voff;
+        if (VEC) {
 #pragma unroll
-        for (int n = 0; n < NV; ++n) {
-          const int c = lane + 32 * n;
-          if (c < VW) acc[n] = fmaf(pj, ldf(vr + c), acc[n]);
+          for (int n = 0; n < NV; n += 2) {
+            const uint32_t u = *reinterpret_cast<const uint32_t*>(vr + 32 * n + 2 * lane);
+            acc[n] = fmaf(pj, bf16lo(u), acc[n]);
+            if (n + 1 < NV) acc[n + 1] = fmaf(pj, bf16hi(u), acc[n + 1]);
+          }
+        } else {
+#pragma unroll
+          for (int n = 0; n < NV; ++n) {
+            const int c = lane + 32 * n;
+            if (c < VW) acc[n] = fmaf(pj, ldf(vr + c), acc[n]);
+          }
         }
       }
     }
@@ -259,7 +285,7 @@ __global__ void __launch_bounds__(HA_WARPS * 32) heads_attention_kernel(const fl
     const float inv = 1.0f / l;
 #pragma unroll
     for (int n = 0; n < NV; ++n) {
-      const int c = lane + 32 * n;
+      const int c = ha_col<VEC>(n, lane);
       if (c < VW) stf(orow + c, acc[n] * inv);
     }
     return;
@@ -274,7 +300,7 @@ __global__ void __launch_bounds__(HA_WARPS * 32) heads_attention_kernel(const fl
   }
 #pragma unroll
   for (int n = 0; n < NV; ++n) {
-    const int c = lane + 32 * n;
+    const int c = ha_col<VEC>(n, lane);
     if (c < VW) as[(size_t)warp * VW + c] = acc[n];
   }
   __syncthreads();
@@ -328,41 +354,46 @@ __device__ __forceinline__ void mma_bf16_16816(float* c, const uint32_t* a, uint
                : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+__device__ __forceinline__ void ldmatrix_x4(uint32_t* r, uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
 __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t* r, uint32_t addr) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
 }
 
-template <int KD, int NO, typename TO>
-__global__ void __launch_bounds__(128) heads_attention_mma_kernel(const float* __restrict__ q, const bf16* __restrict__ k_cache,
+// HPC query heads of one key/value head per CTA (four warps each) share the staged key and value tiles.
+template <int KD, int NO, int HPC, typename TO>
+__global__ void __launch_bounds__(128 * HPC) heads_attention_mma_kernel(const float* __restrict__ q, const bf16* __restrict__ k_cache,
                                                                   const bf16* __restrict__ v_cache, HeadsGeom g,
                                                                   const int32_t* __restrict__ block_table, int bt_stride, int block_size,
                                                                   const PrefillTile* __restrict__ tiles, TO* __restrict__ out) {
   constexpr int D = KD * 16, DV = NO * 8, QS = D + HM_PAD, VS = DV + HM_PAD;
   extern __shared__ __align__(16) unsigned char smraw[];
-  bf16* Qs = reinterpret_cast<bf16*>(smraw);       // [64][QS]
-  bf16* Ks = Qs + HM_ROWS * QS;                    // [64][QS]
+  bf16* Qs = reinterpret_cast<bf16*>(smraw);       // [HPC][64][QS]
+  bf16* Ks = Qs + HPC * HM_ROWS * QS;              // [64][QS]
   bf16* Vs = Ks + HM_KEYS * QS;                    // [64][VS]
   pdl_wait();
   pdl_launch_dependents();
   const PrefillTile tl = tiles[blockIdx.x];
   if (tl.nrows <= 0) return;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gq = lane >> 2, tq = lane & 3;
-  const int a = blockIdx.y, kvh = a / (g.heads / g.kv_heads), vh = g.cross ? (int)blockIdx.z : kvh;
+  constexpr int NT = 128 * HPC;
+  const int warp = (threadIdx.x >> 5) & 3, hl = threadIdx.x >> 7, lane = threadIdx.x & 31, gq = lane >> 2, tq = lane & 3;
+  const int a = blockIdx.y * HPC + hl, kvh = (blockIdx.y * HPC) / (g.heads / g.kv_heads), vh = g.cross ? (int)blockIdx.z : kvh;
   const int krow = g.kv_heads * D, vrow = g.kv_heads * DV;
   // queries: fp32 -> bf16, rows past the tile's end are zero
-  for (int i = threadIdx.x; i < HM_ROWS * (D / 4); i += 128) {
-    const int r = i / (D / 4), c4 = (i - r * (D / 4)) * 4;
+  for (int i = threadIdx.x; i < HPC * HM_ROWS * (D / 4); i += NT) {
+    const int hr = i / (D / 4), c4 = (i - hr * (D / 4)) * 4, h2 = hr / HM_ROWS, r = hr - h2 * HM_ROWS;
     float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (r < tl.nrows) v = *reinterpret_cast<const float4*>(q + ((size_t)(tl.q_row0 + r) * g.heads + a) * D + c4);
+    if (r < tl.nrows) v = *reinterpret_cast<const float4*>(q + ((size_t)(tl.q_row0 + r) * g.heads + blockIdx.y * HPC + h2) * D + c4);
     uint2 pk;
     pk.x = pack_bf16x2(v.x, v.y);
     pk.y = pack_bf16x2(v.z, v.w);
-    *reinterpret_cast<uint2*>(Qs + r * QS + c4) = pk;
+    *reinterpret_cast<uint2*>(Qs + hr * QS + c4) = pk;
   }
   __syncthreads();
   uint32_t qa[KD][4];
   {
-    const bf16* q0 = Qs + (warp * 16 + gq) * QS + 2 * tq;
+    const bf16* q0 = Qs + (hl * HM_ROWS + warp * 16 + gq) * QS + 2 * tq;
 #pragma unroll
     for (int kk = 0; kk < KD; ++kk) {
       qa[kk][0] = *reinterpret_cast<const uint32_t*>(q0 + kk * 16);
@@ -393,13 +424,13 @@ __global__ void __launch_bounds__(128) heads_attention_mma_kernel(const float* _
   for (int vi = 0; vi < total; ++vi) {
     const int key0 = (vi < nA ? vi : tB + (vi - nA)) * HM_KEYS;
     __syncthreads();  // the previous tile's fragments are read
-    for (int i = threadIdx.x; i < HM_KEYS * (D / 8); i += 128) {
+    for (int i = threadIdx.x; i < HM_KEYS * (D / 8); i += NT) {
       const int r = i / (D / 8), c8 = (i - r * (D / 8)) * 8, j = key0 + r;
       uint4 v = make_uint4(0u, 0u, 0u, 0u);
       if (j <= last_key) v = *reinterpret_cast<const uint4*>(k_cache + ((size_t)bt[j / block_size] * block_size + j % block_size) * krow + (size_t)kvh * D + c8);
       *reinterpret_cast<uint4*>(Ks + r * QS + c8) = v;
     }
-    for (int i = threadIdx.x; i < HM_KEYS * (DV / 8); i += 128) {
+    for (int i = threadIdx.x; i < HM_KEYS * (DV / 8); i += NT) {
       const int r = i / (DV / 8), c8 = (i - r * (DV / 8)) * 8, j = key0 + r;
       uint4 v = make_uint4(0u, 0u, 0u, 0u);
       if (j <= last_key) v = *reinterpret_cast<const uint4*>(v_cache + ((size_t)bt[j / block_size] * block_size + j % block_size) * vrow + (size_t)vh * DV + c8);
@@ -410,24 +441,44 @@ __global__ void __launch_bounds__(128) heads_attention_mma_kernel(const float* _
 #pragma unroll
     for (int n = 0; n < HM_KEYS / 8; ++n) {
       sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.f;
-      const bf16* kb = Ks + (n * 8 + gq) * QS + 2 * tq;
+      const uint32_t kb = smem_u32(Ks + (n * 8 + (lane & 7)) * QS + (lane >> 3) * 8);   // four 8 x 8 blocks: two k-steps of one key group
 #pragma unroll
-      for (int kk = 0; kk < KD; ++kk)
-        mma_bf16_16816(sc[n], qa[kk], *reinterpret_cast<const uint32_t*>(kb + kk * 16), *reinterpret_cast<const uint32_t*>(kb + kk * 16 + 8));
+      for (int kk = 0; kk < KD; kk += 2) {
+        uint32_t kf[4];
+        ldmatrix_x4(kf, kb + kk * 16 * 2);
+        mma_bf16_16816(sc[n], qa[kk], kf[0], kf[1]);
+        mma_bf16_16816(sc[n], qa[kk + 1], kf[2], kf[3]);
+      }
     }
-    // scale, distance penalty, mask; row maxima over the quad
+    // scale, distance penalty, mask; row maxima over the quad.  A tile that every row of the CTA sees whole needs no mask.
     float t0 = -INFINITY, t1 = -INFINITY;
+    const bool whole = tl.nrows == HM_ROWS && key0 + HM_KEYS - 1 <= tl.q_pos0 &&
+                       (g.window <= 0 || last_key - key0 < g.window || key0 + HM_KEYS - 1 < g.keep_first);
+    if (whole) {
 #pragma unroll
-    for (int n = 0; n < HM_KEYS / 8; ++n) {
+      for (int n = 0; n < HM_KEYS / 8; ++n) {
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int j = key0 + n * 8 + 2 * tq + (e & 1);
-        const int p = (e & 2) ? p1 : p0;
-        const bool ok = ((e & 2) ? live1 : live0) && j <= p && (g.window <= 0 || p - j < g.window || j < g.keep_first);
-        const float v = ok ? sc[n][e] * g.scale - slope * (float)(p - j) : -INFINITY;
-        sc[n][e] = v;
-        if (e & 2) t1 = fmaxf(t1, v);
-        else t0 = fmaxf(t0, v);
+        for (int e = 0; e < 4; ++e) {
+          const int j = key0 + n * 8 + 2 * tq + (e & 1);
+          const float v = sc[n][e] * g.scale - slope * (float)(((e & 2) ? p1 : p0) - j);
+          sc[n][e] = v;
+          if (e & 2) t1 = fmaxf(t1, v);
+          else t0 = fmaxf(t0, v);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int n = 0; n < HM_KEYS / 8; ++n) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int j = key0 + n * 8 + 2 * tq + (e & 1);
+          const int p = (e & 2) ? p1 : p0;
+          const bool ok = ((e & 2) ? live1 : live0) && j <= p && (g.window <= 0 || p - j < g.window || j < g.keep_first);
+          const float v = ok ? sc[n][e] * g.scale - slope * (float)(p - j) : -INFINITY;
+          sc[n][e] = v;
+          if (e & 2) t1 = fmaxf(t1, v);
+          else t0 = fmaxf(t0, v);
+        }
       }
     }
     t0 = fmaxf(t0, __shfl_xor_sync(0xffffffffu, t0, 1));
@@ -495,14 +546,22 @@ __global__ void __launch_bounds__(128) heads_attention_mma_kernel(const float* _
   }
 }
 
+template <int KD, int NO, int HPC, typename TO>
+int launch_attention_mma_h(const float* q, const bf16* k, const bf16* v, const HeadsGeom& g, const int32_t* bt, int bt_stride, int block_size,
+                           const PrefillTile* tiles, int ntiles, TO* out, cudaStream_t s) {
+  const size_t smem = ((size_t)(HPC + 1) * HM_ROWS * (KD * 16 + HM_PAD) + (size_t)HM_KEYS * (NO * 8 + HM_PAD)) * sizeof(bf16);
+  auto kern = heads_attention_mma_kernel<KD, NO, HPC, TO>;
+  if (smem > 48 * 1024) B2_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  B2_CUDA_OK(b2_launch(kern, dim3(ntiles, g.heads / HPC, g.cross ? g.kv_heads : 1), dim3(128 * HPC), smem, s, q, k, v, g, bt, bt_stride, block_size,
+                       tiles, out));
+  return 0;
+}
 template <int KD, int NO, typename TO>
 int launch_attention_mma_t(const float* q, const bf16* k, const bf16* v, const HeadsGeom& g, const int32_t* bt, int bt_stride, int block_size,
                            const PrefillTile* tiles, int ntiles, TO* out, cudaStream_t s) {
-  const size_t smem = ((size_t)2 * HM_ROWS * (KD * 16 + HM_PAD) + (size_t)HM_KEYS * (NO * 8 + HM_PAD)) * sizeof(bf16);
-  auto kern = heads_attention_mma_kernel<KD, NO, TO>;
-  if (smem > 48 * 1024) B2_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  B2_CUDA_OK(b2_launch(kern, dim3(ntiles, g.heads, g.cross ? g.kv_heads : 1), dim3(128), smem, s, q, k, v, g, bt, bt_stride, block_size, tiles, out));
-  return 0;
+  if ((g.heads / g.kv_heads) % 2 == 0)   // two query heads of a key/value head share its staged tiles
+    return launch_attention_mma_h<KD, NO, 2, TO>(q, k, v, g, bt, bt_stride, block_size, tiles, ntiles, out, s);
+  return launch_attention_mma_h<KD, NO, 1, TO>(q, k, v, g, bt, bt_stride, block_size, tiles, ntiles, out, s);
 }
 
 // 1 = launched; 0 = the sizes have no tensor-core form (the caller takes the plain kernel)
@@ -519,13 +578,13 @@ int launch_attention_mma(const float* q, const bf16* k, const bf16* v, const Hea
   return 0;
 }
 
-template <typename TC, typename TO, bool DECODE>
+template <typename TC, typename TO, bool DECODE, bool VEC>
 int launch_attention_nv(int nv, dim3 grid, size_t smem, cudaStream_t s, const float* q, const TC* k, const TC* v, const HeadsGeom& g,
                         const int32_t* bt, int bt_stride, int block_size, const PrefillTile* tiles, const int32_t* positions,
                         const int32_t* seq_lens, TO* out) {
 #define HA_CASE(NVV)                                                                                                                   \
   if (nv <= NVV) {                                                                                                                     \
-    auto kern = heads_attention_kernel<TC, TO, NVV, DECODE>;                                                                           \
+    auto kern = heads_attention_kernel<TC, TO, NVV, DECODE, VEC>;                                                                      \
     if (smem > 48 * 1024) B2_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));              \
     B2_CUDA_OK(b2_launch(kern, grid, dim3(HA_WARPS * 32), smem, s, q, k, v, g, bt, bt_stride, block_size, tiles, positions, seq_lens, out)); \
     return 0;                                                                                                                          \
@@ -541,14 +600,22 @@ int launch_attention_t(const float* q, const void* k, const void* v, const Heads
                        const PrefillTile* tiles, int ntiles, const int32_t* positions, const int32_t* seq_lens, void* out, int T,
                        cudaStream_t s) {
   const int VW = g.cross ? g.kv_heads * g.vdim : g.vdim, nv = (VW + 31) / 32;
+  constexpr bool can_vec = sizeof(TC) == 2;
+  const bool vec = can_vec && g.dim % 8 == 0 && VW % 64 == 0 && g.vdim % 2 == 0;
   if (tiles != nullptr) {
     const size_t smem = (size_t)HA_WARPS * g.dim * sizeof(float);
-    return launch_attention_nv<TC, TO, false>(nv, dim3(ntiles * 8, g.heads), smem, s, q, (const TC*)k, (const TC*)v, g, bt, bt_stride,
-                                              block_size, tiles, positions, seq_lens, (TO*)out);
+    if (vec)
+      return launch_attention_nv<TC, TO, false, can_vec>(nv, dim3(ntiles * 8, g.heads), smem, s, q, (const TC*)k, (const TC*)v, g, bt, bt_stride,
+                                                         block_size, tiles, positions, seq_lens, (TO*)out);
+    return launch_attention_nv<TC, TO, false, false>(nv, dim3(ntiles * 8, g.heads), smem, s, q, (const TC*)k, (const TC*)v, g, bt, bt_stride,
+                                                     block_size, tiles, positions, seq_lens, (TO*)out);
   }
   const size_t smem = ((size_t)g.dim + 2 * HA_WARPS + (size_t)HA_WARPS * VW) * sizeof(float);
-  return launch_attention_nv<TC, TO, true>(nv, dim3(T, g.heads), smem, s, q, (const TC*)k, (const TC*)v, g, bt, bt_stride, block_size,
-                                           nullptr, positions, seq_lens, (TO*)out);
+  if (vec)
+    return launch_attention_nv<TC, TO, true, can_vec>(nv, dim3(T, g.heads), smem, s, q, (const TC*)k, (const TC*)v, g, bt, bt_stride, block_size,
+                                                      nullptr, positions, seq_lens, (TO*)out);
+  return launch_attention_nv<TC, TO, true, false>(nv, dim3(T, g.heads), smem, s, q, (const TC*)k, (const TC*)v, g, bt, bt_stride, block_size,
+                                                  nullptr, positions, seq_lens, (TO*)out);
 }
 
 }  // namespace
