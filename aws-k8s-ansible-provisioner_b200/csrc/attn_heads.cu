@@ -256,20 +256,41 @@ __global__ void __launch_bounds__(HA_WARPS * 32) heads_attention_kernel(const fl
       for (int n = 0; n < NV; ++n) acc[n] *= corr;
       m = mn;
       unsigned mask = __ballot_sync(0xffffffffu, vis);
+      if (VEC) {
+        // every key of the tile, eight at a time so that their loads are in flight together; a key that is not seen has
+        // weight 0 and slot 0 (the null page: zeros)
+        const unsigned slot32 = (unsigned)slot;
+#pragma unroll 1
+        for (int j0 = 0; j0 < 32; j0 += 8) {
+          if (((mask >> j0) & 0xffu) == 0) continue;
+          uint32_t u[8][(NV + 1) / 2];
+          float pj[8];
+#pragma unroll
+          for (int x = 0; x < 8; ++x) {
+            pj[x] = __shfl_sync(0xffffffffu, p, j0 + x);
+            const size_t sj = __shfl_sync(0xffffffffu, slot32, j0 + x);
+            const TC* vr = v_cache + sj * vrow + voff;
+#pragma unroll
+            for (int n = 0; n < NV; n += 2) u[x][n >> 1] = *reinterpret_cast<const uint32_t*>(vr + 32 * n + 2 * lane);
+          }
+#pragma unroll
+          for (int x = 0; x < 8; ++x) {
+#pragma unroll
+            for (int n = 0; n < NV; n += 2) {
+              acc[n] = fmaf(pj[x], bf16lo(u[x][n >> 1]), acc[n]);
+              if (n + 1 < NV) acc[n + 1] = fmaf(pj[x], bf16hi(u[x][n >> 1]), acc[n + 1]);
+            }
+          }
+        }
+        mask = 0;
+      }
       while (mask) {
         const int jj = __ffs(mask) - 1;
         mask &= mask - 1;
         const float pj = __shfl_sync(0xffffffffu, p, jj);
         const size_t sj = __shfl_sync(0xffffffffu, (unsigned long long)slot, jj);
         const TC* vr = v_cache + sj * vrow + voff;
-        if (VEC) {
-#pragma unroll
-          for (int n = 0; n < NV; n += 2) {
-            const uint32_t u = *reinterpret_cast<const uint32_t*>(vr + 32 * n + 2 * lane);
-            acc[n] = fmaf(pj, bf16lo(u), acc[n]);
-            if (n + 1 < NV) acc[n + 1] = fmaf(pj, bf16hi(u), acc[n + 1]);
-          }
-        } else {
+        {
 #pragma unroll
           for (int n = 0; n < NV; ++n) {
             const int c = lane + 32 * n;
@@ -370,8 +391,8 @@ __global__ void __launch_bounds__(128 * HPC) heads_attention_mma_kernel(const fl
   constexpr int D = KD * 16, DV = NO * 8, QS = D + HM_PAD, VS = DV + HM_PAD;
   extern __shared__ __align__(16) unsigned char smraw[];
   bf16* Qs = reinterpret_cast<bf16*>(smraw);       // [HPC][64][QS]
-  bf16* Ks = Qs + HPC * HM_ROWS * QS;              // [64][QS]
-  bf16* Vs = Ks + HM_KEYS * QS;                    // [64][VS]
+  bf16* Ks = Qs + HPC * HM_ROWS * QS;              // [2][64][QS]: a tile is loaded while the one before it is used
+  bf16* Vs = Ks + 2 * HM_KEYS * QS;                // [2][64][VS]
   pdl_wait();
   pdl_launch_dependents();
   const PrefillTile tl = tiles[blockIdx.x];
@@ -421,27 +442,42 @@ __global__ void __launch_bounds__(128 * HPC) heads_attention_mma_kernel(const fl
   const int total = nA + (last_tile - tB + 1);
   const int32_t* bt = block_table + (size_t)tl.bt_row * bt_stride;
   constexpr float LOG2E = 1.4426950408889634f;
-  for (int vi = 0; vi < total; ++vi) {
+  // 16-byte asynchronous copies; rows past the sequence's end are filled with zeros (source size 0)
+  auto stage = [&](int vi, int buf) {
     const int key0 = (vi < nA ? vi : tB + (vi - nA)) * HM_KEYS;
-    __syncthreads();  // the previous tile's fragments are read
+    bf16* kd = Ks + buf * HM_KEYS * QS;
+    bf16* vd = Vs + buf * HM_KEYS * VS;
     for (int i = threadIdx.x; i < HM_KEYS * (D / 8); i += NT) {
       const int r = i / (D / 8), c8 = (i - r * (D / 8)) * 8, j = key0 + r;
-      uint4 v = make_uint4(0u, 0u, 0u, 0u);
-      if (j <= last_key) v = *reinterpret_cast<const uint4*>(k_cache + ((size_t)bt[j / block_size] * block_size + j % block_size) * krow + (size_t)kvh * D + c8);
-      *reinterpret_cast<uint4*>(Ks + r * QS + c8) = v;
+      const bool in = j <= last_key;
+      const bf16* src = k_cache + ((size_t)(in ? bt[j / block_size] : 0) * block_size + j % block_size) * krow + (size_t)kvh * D + c8;
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(kd + r * QS + c8)), "l"(src), "r"(in ? 16 : 0) : "memory");
     }
     for (int i = threadIdx.x; i < HM_KEYS * (DV / 8); i += NT) {
       const int r = i / (DV / 8), c8 = (i - r * (DV / 8)) * 8, j = key0 + r;
-      uint4 v = make_uint4(0u, 0u, 0u, 0u);
-      if (j <= last_key) v = *reinterpret_cast<const uint4*>(v_cache + ((size_t)bt[j / block_size] * block_size + j % block_size) * vrow + (size_t)vh * DV + c8);
-      *reinterpret_cast<uint4*>(Vs + r * VS + c8) = v;
+      const bool in = j <= last_key;
+      const bf16* src = v_cache + ((size_t)(in ? bt[j / block_size] : 0) * block_size + j % block_size) * vrow + (size_t)vh * DV + c8;
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(vd + r * VS + c8)), "l"(src), "r"(in ? 16 : 0) : "memory");
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  stage(0, 0);
+  for (int vi = 0; vi < total; ++vi) {
+    const int key0 = (vi < nA ? vi : tB + (vi - nA)) * HM_KEYS;
+    const bf16* Kt = Ks + (vi & 1) * HM_KEYS * QS;
+    const bf16* Vt = Vs + (vi & 1) * HM_KEYS * VS;
+    if (vi + 1 < total) {
+      stage(vi + 1, (vi + 1) & 1);   // its buffer was last read two tiles ago (the barrier at the end of that iteration)
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
     }
     __syncthreads();
     float sc[HM_KEYS / 8][4];
 #pragma unroll
     for (int n = 0; n < HM_KEYS / 8; ++n) {
       sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.f;
-      const uint32_t kb = smem_u32(Ks + (n * 8 + (lane & 7)) * QS + (lane >> 3) * 8);   // four 8 x 8 blocks: two k-steps of one key group
+      const uint32_t kb = smem_u32(Kt + (n * 8 + (lane & 7)) * QS + (lane >> 3) * 8);   // four 8 x 8 blocks: two k-steps of one key group
 #pragma unroll
       for (int kk = 0; kk < KD; kk += 2) {
         uint32_t kf[4];
@@ -510,7 +546,7 @@ __global__ void __launch_bounds__(128 * HPC) heads_attention_mma_kernel(const fl
     }
 #pragma unroll
     for (int kk = 0; kk < HM_KEYS / 16; ++kk) {
-      const uint32_t vbase = smem_u32(Vs + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * VS + (lane >> 4) * 8);
+      const uint32_t vbase = smem_u32(Vt + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * VS + (lane >> 4) * 8);
 #pragma unroll
       for (int n = 0; n < NO; n += 2) {
         uint32_t vb[4];
@@ -519,6 +555,7 @@ __global__ void __launch_bounds__(128 * HPC) heads_attention_mma_kernel(const fl
         mma_bf16_16816(o[n + 1], pa[kk], vb[2], vb[3]);
       }
     }
+    __syncthreads();  // every warp is done with this buffer before the tile after the next is copied into it
   }
   // row sums over the quad, then the output
   l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
@@ -549,7 +586,7 @@ __global__ void __launch_bounds__(128 * HPC) heads_attention_mma_kernel(const fl
 template <int KD, int NO, int HPC, typename TO>
 int launch_attention_mma_h(const float* q, const bf16* k, const bf16* v, const HeadsGeom& g, const int32_t* bt, int bt_stride, int block_size,
                            const PrefillTile* tiles, int ntiles, TO* out, cudaStream_t s) {
-  const size_t smem = ((size_t)(HPC + 1) * HM_ROWS * (KD * 16 + HM_PAD) + (size_t)HM_KEYS * (NO * 8 + HM_PAD)) * sizeof(bf16);
+  const size_t smem = ((size_t)(HPC + 2) * HM_ROWS * (KD * 16 + HM_PAD) + (size_t)2 * HM_KEYS * (NO * 8 + HM_PAD)) * sizeof(bf16);
   auto kern = heads_attention_mma_kernel<KD, NO, HPC, TO>;
   if (smem > 48 * 1024) B2_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   B2_CUDA_OK(b2_launch(kern, dim3(ntiles, g.heads / HPC, g.cross ? g.kv_heads : 1), dim3(128 * HPC), smem, s, q, k, v, g, bt, bt_stride, block_size,
