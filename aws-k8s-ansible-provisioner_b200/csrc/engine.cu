@@ -1063,7 +1063,9 @@ int forward_heads_list(b2_engine* e, int T, int ntiles, int nlast) {
                 conv ? 1 : 0, KEDASUN_SLOPE_EXP, sp.window, sp.keep_first, conv ? 1 : 0};
     char* kc = e->regions[L.cache_region].base;
     char* vc = e->regions[L.v_region].base;
-    {
+    const bool has_ff = sp.ff == B2_FF_CLAMPED_GATED;
+    const float* next_gain1 = l + 1 < c.num_layers && e->skip_mask == 0 ? e->ll[l + 1].gain1 : nullptr;  // the norm behind a sublayer also does the one in front of the next
+    if (l == 0 || e->skip_mask != 0) {
       KL k(e, B2K_NORM);
       if (!k.skip()) B2_TRY(launch_group_norm(e->l_h, L.gain1, e->l_x1, f, T, W, groups, c.rms_eps, nullptr, st));
     }
@@ -1090,11 +1092,12 @@ int forward_heads_list(b2_engine* e, int T, int ntiles, int nlast) {
       if (!k.skip()) B2_TRY(list_dense(e, e->l_av, L.wo, e->l_mix, T, W, sp.heads * sp.vdim, 1.f));
     }
     {
-      KL k(e, B2K_NORM);  // h += n1b(mixer output + bias)
-      if (!k.skip()) B2_TRY(launch_group_norm_add(e->l_h, e->l_mix, L.o_bias, L.gain1b, T, W, groups, c.rms_eps, st));
+      KL k(e, B2K_NORM);  // h += n1b(mixer output + bias); x1 = the next sublayer's input norm
+      const float* gn = e->skip_mask != 0 ? nullptr : has_ff ? L.gain2 : next_gain1;
+      if (!k.skip()) B2_TRY(launch_group_norm_add(e->l_h, e->l_mix, L.o_bias, L.gain1b, T, W, groups, c.rms_eps, st, gn, gn ? e->l_x1 : nullptr, f));
     }
-    if (sp.ff == B2_FF_CLAMPED_GATED) {
-      {
+    if (has_ff) {
+      if (e->skip_mask != 0) {
         KL k(e, B2K_NORM);
         if (!k.skip()) B2_TRY(launch_group_norm(e->l_h, L.gain2, e->l_x1, f, T, W, groups, c.rms_eps, nullptr, st));
       }
@@ -1112,7 +1115,7 @@ int forward_heads_list(b2_engine* e, int T, int ntiles, int nlast) {
       }
       {
         KL k(e, B2K_NORM);
-        if (!k.skip()) B2_TRY(launch_group_norm_add(e->l_h, e->l_mix, nullptr, L.gain2b, T, W, groups, c.rms_eps, st));
+        if (!k.skip()) B2_TRY(launch_group_norm_add(e->l_h, e->l_mix, nullptr, L.gain2b, T, W, groups, c.rms_eps, st, next_gain1, next_gain1 ? e->l_x1 : nullptr, f));
       }
     }
     dbg(l + 1);

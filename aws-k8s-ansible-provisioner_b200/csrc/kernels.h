@@ -258,8 +258,10 @@ int launch_embed_scaled(const int32_t* ids, const void* table, int table_f32, fl
 // x[t] = norm(h[rows ? rows[t] : t]) * gain, x fp32 or bf16
 int launch_group_norm(const float* h, const float* gain, void* x, int x_f32, int T, int W, int groups, float eps, const int32_t* rows,
                       cudaStream_t s);
-// h[t] += norm(y[t] + bias) * gain  (bias may be null): the norm behind a sublayer and the residual add in one pass
-int launch_group_norm_add(float* h, const float* y, const float* bias, const float* gain, int T, int W, int groups, float eps, cudaStream_t s);
+// h[t] += norm(y[t] + bias) * gain  (bias may be null): the norm behind a sublayer and the residual add in one pass; with gain_next
+// the norm in front of the next sublayer as well, x_next[t] = norm(h[t]) * gain_next (fp32 or bf16)
+int launch_group_norm_add(float* h, const float* y, const float* bias, const float* gain, int T, int W, int groups, float eps, cudaStream_t s,
+                          const float* gain_next = nullptr, void* x_next = nullptr, int x_f32 = 0);
 // act[t][i] = g * sigmoid(sharp * g) * (u + 1), g = min(gu[t][i], limit), u = clamp(gu[t][F + i], -limit, limit); gu fp32 [T][2F]
 int launch_clamped_gate(const float* gu, void* act, int act_f32, int T, int F, float limit, float sharp, cudaStream_t s);
 

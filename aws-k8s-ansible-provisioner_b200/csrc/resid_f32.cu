@@ -121,11 +121,14 @@ __global__ void __launch_bounds__(128) embed_scaled_kernel(const int32_t* __rest
   for (int i = threadIdx.x; i < W; i += 128) h[(size_t)t * W + i] = (float)row[i] * scale;
 }
 
-// One CTA per token, one warp per piece (pieces round robin over the four warps).  ADD: h += norm(y + bias) * gain.
+// One CTA per token, one warp per piece (pieces round robin over the four warps).  ADD: h += norm(y + bias) * gain, and when
+// gain_next is given the norm in front of the next sublayer follows at once, x = norm(h) * gain_next (the pieces of both
+// norms are the same, so the warp that updated a piece normalises it).
 template <typename TX, bool ADD>
 __global__ void __launch_bounds__(128) group_norm_kernel(const float* __restrict__ src, const float* __restrict__ bias,
                                                          const float* __restrict__ gain, TX* __restrict__ x, float* __restrict__ h, int W,
-                                                         int groups, float eps, const int32_t* __restrict__ rows) {
+                                                         int groups, float eps, const int32_t* __restrict__ rows,
+                                                         const float* __restrict__ gain_next) {
   pdl_wait();
   pdl_launch_dependents();
   const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -140,10 +143,21 @@ __global__ void __launch_bounds__(128) group_norm_kernel(const float* __restrict
     }
     ss = warp_sum(ss);
     const float r = 1.0f / sqrtf(ss / (float)piece + eps);
+    float ss2 = 0.f;
     for (int i = lane; i < piece; i += 32) {
       const float v = (row[o + i] + (bias ? bias[o + i] : 0.f)) * r * gain[o + i];
-      if (ADD) h[(size_t)t * W + o + i] += v;
-      else x[(size_t)t * W + o + i] = (TX)v;
+      if (ADD) {
+        const float hn = h[(size_t)t * W + o + i] + v;
+        h[(size_t)t * W + o + i] = hn;
+        ss2 = fmaf(hn, hn, ss2);
+      } else {
+        x[(size_t)t * W + o + i] = (TX)v;
+      }
+    }
+    if (ADD && gain_next != nullptr) {
+      ss2 = warp_sum(ss2);
+      const float r2 = 1.0f / sqrtf(ss2 / (float)piece + eps);
+      for (int i = lane; i < piece; i += 32) x[(size_t)t * W + o + i] = (TX)(h[(size_t)t * W + o + i] * r2 * gain_next[o + i]);  // its own writes
     }
   }
 }
@@ -175,16 +189,23 @@ int launch_group_norm(const float* h, const float* gain, void* x, int x_f32, int
   if (T <= 0) return 0;
   B2_REQUIRE(groups >= 1 && W % groups == 0, "group_norm: width %d is not %d equal pieces", W, groups);
   if (x_f32)
-    B2_CUDA_OK(b2_launch(group_norm_kernel<float, false>, dim3(T), dim3(128), 0, s, h, (const float*)nullptr, gain, (float*)x, (float*)nullptr, W, groups, eps, rows));
+    B2_CUDA_OK(b2_launch(group_norm_kernel<float, false>, dim3(T), dim3(128), 0, s, h, (const float*)nullptr, gain, (float*)x, (float*)nullptr, W, groups, eps, rows,
+                         (const float*)nullptr));
   else
-    B2_CUDA_OK(b2_launch(group_norm_kernel<bf16, false>, dim3(T), dim3(128), 0, s, h, (const float*)nullptr, gain, (bf16*)x, (float*)nullptr, W, groups, eps, rows));
+    B2_CUDA_OK(b2_launch(group_norm_kernel<bf16, false>, dim3(T), dim3(128), 0, s, h, (const float*)nullptr, gain, (bf16*)x, (float*)nullptr, W, groups, eps, rows,
+                         (const float*)nullptr));
   return 0;
 }
 
-int launch_group_norm_add(float* h, const float* y, const float* bias, const float* gain, int T, int W, int groups, float eps, cudaStream_t s) {
+int launch_group_norm_add(float* h, const float* y, const float* bias, const float* gain, int T, int W, int groups, float eps, cudaStream_t s,
+                          const float* gain_next, void* x_next, int x_f32) {
   if (T <= 0) return 0;
   B2_REQUIRE(groups >= 1 && W % groups == 0, "group_norm: width %d is not %d equal pieces", W, groups);
-  B2_CUDA_OK(b2_launch(group_norm_kernel<float, true>, dim3(T), dim3(128), 0, s, y, bias, gain, (float*)nullptr, h, W, groups, eps, (const int32_t*)nullptr));
+  B2_REQUIRE((gain_next == nullptr) == (x_next == nullptr), "group_norm_add: the following norm needs its gain and its output");
+  if (x_f32 || x_next == nullptr)
+    B2_CUDA_OK(b2_launch(group_norm_kernel<float, true>, dim3(T), dim3(128), 0, s, y, bias, gain, (float*)x_next, h, W, groups, eps, (const int32_t*)nullptr, gain_next));
+  else
+    B2_CUDA_OK(b2_launch(group_norm_kernel<bf16, true>, dim3(T), dim3(128), 0, s, y, bias, gain, (bf16*)x_next, h, W, groups, eps, (const int32_t*)nullptr, gain_next));
   return 0;
 }
 
