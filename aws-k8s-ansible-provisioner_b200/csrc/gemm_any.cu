@@ -441,10 +441,12 @@ __device__ __forceinline__ void mma_16816(float* d, unsigned a0, unsigned a1, un
                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// NT: eight-row token tiles per pass (rows per pass = 8 * NT); U: k chunks in flight per warp
-template <typename TC, int NT, int U>
-__global__ void __launch_bounds__(128) gemm_any_rows_mma_kernel(AnyGemm g) {
-  __shared__ float red[4][NT][32][4];
+// NT: eight-row token tiles per pass (rows per pass = 8 * NT); U: k chunks in flight per warp; NW: warps that split K (four when
+// the output is wide enough to give every SM several CTAs; eight or sixteen for narrow outputs, whose few CTAs would otherwise
+// leave most of an SM's load slots empty -- the choice depends on N, K and the batch count only, never on the rows)
+template <typename TC, int NT, int U, int NW>
+__global__ void __launch_bounds__(32 * NW) gemm_any_rows_mma_kernel(AnyGemm g) {
+  __shared__ float red[NW][NT][32][4];
   pdl_wait();
   pdl_launch_dependents();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, gq = lane >> 2, c = lane & 3;
@@ -480,11 +482,11 @@ __global__ void __launch_bounds__(128) gemm_any_rows_mma_kernel(AnyGemm g) {
     for (int t = 0; t < NT; ++t)
 #pragma unroll
       for (int i = 0; i < 4; ++i) acc[t][i] = 0.f;
-    for (int ch0 = warp; ch0 < nchunk; ch0 += 4 * U) {
+    for (int ch0 = warp; ch0 < nchunk; ch0 += NW * U) {
       uint4 wl[U], wh[U], tv[U][NT];
 #pragma unroll
       for (int u = 0; u < U; ++u) {
-        const int k = (ch0 + 4 * u) << 5;
+        const int k = (ch0 + NW * u) << 5;
         const bool in = k + c * 8 < K;   // K is a multiple of 8: a lane's eight elements are inside or outside together
         wl[u] = in ? ld_stream(w_lo + k) : make_uint4(0, 0, 0, 0);
         wh[u] = in ? ld_stream(w_hi + k) : make_uint4(0, 0, 0, 0);
@@ -506,12 +508,14 @@ __global__ void __launch_bounds__(128) gemm_any_rows_mma_kernel(AnyGemm g) {
       *reinterpret_cast<float4*>(&red[warp][t][lane][0]) = make_float4(acc[t][0], acc[t][1], acc[t][2], acc[t][3]);
     __syncthreads();
     // fragment element i of lane (g, c): weight row g + 8 * (i / 2), token row 2c + (i % 2)
-    for (int idx = tid; idx < NT * 128; idx += 128) {
+    for (int idx = tid; idx < NT * 128; idx += 32 * NW) {
       const int t = idx >> 7, rem = idx & 127, wr = rem & 15, tk = rem >> 4;   // consecutive threads -> consecutive weight rows
       const int ln = (wr & 7) * 4 + (tk >> 1), i = (wr >> 3) * 2 + (tk & 1);
       const int r = r0 + t * 8 + tk, n = n0 + wr;
       if (r >= row_hi || n >= g.N) continue;
       float v = ((red[0][t][ln][i] + red[1][t][ln][i]) + red[2][t][ln][i]) + red[3][t][ln][i];
+#pragma unroll
+      for (int w = 4; w < NW; ++w) v += red[w][t][ln][i];
       v *= g.alpha;
       TC* dst = C + (size_t)r * g.ldc + n;
       if (g.epilogue == ANY_EPI_RELU2) {
@@ -540,10 +544,20 @@ int launch_rows_mma(const AnyGemm& g, int groups, int batch, cudaStream_t s) {
   // rows per pass: a ragged group's count is only known on the device (16 covers the usual handful per expert; more rows
   // take more passes over weights that are then in L2)
   const int rows = groups > 0 ? 16 : g.M;
-  if (rows <= 8) B2_CUDA_OK(b2_launch(gemm_any_rows_mma_kernel<TC, 1, 4>, grid, dim3(128), 0, s, g));
-  else if (rows <= 16) B2_CUDA_OK(b2_launch(gemm_any_rows_mma_kernel<TC, 2, 4>, grid, dim3(128), 0, s, g));
-  else if (rows <= 32) B2_CUDA_OK(b2_launch(gemm_any_rows_mma_kernel<TC, 4, 2>, grid, dim3(128), 0, s, g));
-  else B2_CUDA_OK(b2_launch(gemm_any_rows_mma_kernel<TC, 8, 1>, grid, dim3(128), 0, s, g));
+  const long ctas = (long)grid.x * grid.y * grid.z;
+  const int nchunk = (g.K + 31) / 32;
+  const int nw = (groups > 0 || ctas >= 4 * 148 || nchunk < 32) ? 4 : (ctas >= 2 * 148 || nchunk < 64) ? 8 : 16;
+#define ROWS_MMA_LAUNCH(NW)                                                                                        \
+  do {                                                                                                             \
+    if (rows <= 8) B2_CUDA_OK(b2_launch(gemm_any_rows_mma_kernel<TC, 1, 4, NW>, grid, dim3(32 * NW), 0, s, g));    \
+    else if (rows <= 16) B2_CUDA_OK(b2_launch(gemm_any_rows_mma_kernel<TC, 2, 4, NW>, grid, dim3(32 * NW), 0, s, g)); \
+    else if (rows <= 32) B2_CUDA_OK(b2_launch(gemm_any_rows_mma_kernel<TC, 4, 2, NW>, grid, dim3(32 * NW), 0, s, g)); \
+    else B2_CUDA_OK(b2_launch(gemm_any_rows_mma_kernel<TC, 8, 1, (NW > 8 ? 8 : NW)>, grid, dim3(32 * (NW > 8 ? 8 : NW)), 0, s, g)); /* 48 KB of static shared memory */ \
+  } while (0)
+  if (nw == 4) ROWS_MMA_LAUNCH(4);
+  else if (nw == 8) ROWS_MMA_LAUNCH(8);
+  else ROWS_MMA_LAUNCH(16);
+#undef ROWS_MMA_LAUNCH
   return 0;
 }
 
