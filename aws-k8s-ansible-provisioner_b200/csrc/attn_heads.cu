@@ -18,8 +18,8 @@
 // its ring.  Only what is stored in a bf16 cache or handed to a bf16 product is rounded.
 //
 // Kernels:
-//   heads_finish      what follows the fused q | k | v (| gate) projection: bias, convolution, rotary or unit-RMS norm,
-//                     value mixing, cache row write, fp32 queries
+//   heads_finish      what follows the fused q | k | v (| gate) projection, one CTA per (token, head): bias, convolution, rotary or
+//                     unit-RMS norm, value mixing, cache row write, fp32 queries
 //   conv_tail_store   the ring update, after every token of the step has read the ring
 //   heads_attention   one warp per (query token, head) for prompt portions; for a decode step the eight warps of a CTA
 //                     split the keys of one (sequence, head) and merge.  Tiles of 32 keys: lane j scores key j, then lane
@@ -57,7 +57,8 @@ __device__ __forceinline__ void pair_cos_sin(int pos, int i, int dims, float bas
   *s = (float)sd;
 }
 
-// One CTA per token.  proj [T][ld] fp32: q (heads * dim) | k (kv_heads * dim) | v (kv_heads * vdim) | anything else.
+// One CTA per (token, head): blockIdx.y names a query head, then a key head, then a value head.
+// proj [T][ld] fp32: q (heads * dim) | k (kv_heads * dim) | v (kv_heads * vdim) | anything else.
 template <typename TC>
 __global__ void __launch_bounds__(128) heads_finish_kernel(const float* __restrict__ proj, int ld, HeadsGeom g, const float* __restrict__ bias,
                                                            const float* __restrict__ conv_w, const float* __restrict__ ring,
@@ -66,70 +67,84 @@ __global__ void __launch_bounds__(128) heads_finish_kernel(const float* __restri
                                                            int vmix_mode, const float* __restrict__ vmix_lambda, float* __restrict__ v_first,
                                                            float* __restrict__ q_out, TC* __restrict__ k_cache, TC* __restrict__ v_cache) {
   extern __shared__ float sm[];
+  __shared__ float red[4];
   pdl_wait();
   pdl_launch_dependents();
-  const int t = blockIdx.x;
+  const int t = blockIdx.x, u = blockIdx.y;
   const int slot = slots[t];
   if (slot < 0) return;  // padding row of a decode bucket
   const int pos = positions[t];
   const int nq = g.heads * g.dim, nk = g.kv_heads * g.dim, nv = g.kv_heads * g.vdim, C = nq + nk + nv;
-  float* y = sm;            // [C] the token's q | k | v after bias and convolution
-  float* cs = sm + C;       // [rot_dims] cos | sin
-  const int half = g.rot_dims / 2;
+  const bool is_v = u >= g.heads + g.kv_heads;
+  const int width = is_v ? g.vdim : g.dim;
+  const int c0 = is_v ? nq + nk + (u - g.heads - g.kv_heads) * g.vdim : u * g.dim;   // first channel of this head in q | k | v
+  float* y = sm;              // [width] the head after bias and convolution
+  float* cs = sm + width;     // [rot_dims] cos | sin
+  const int half = is_v ? 0 : g.rot_dims / 2;
   for (int i = threadIdx.x; i < half; i += 128) pair_cos_sin(pos, i, g.rot_dims, g.rot_base, &cs[i], &cs[half + i]);
   const float* row = proj + (size_t)t * ld;
   if (g.conv_taps > 0) {
     const int taps = g.conv_taps, back = t - row_first[t];
     const float* rg = ring + (size_t)row_seq[t] * taps * C;
-    for (int c = threadIdx.x; c < C; c += 128) {
+    for (int i = threadIdx.x; i < width; i += 128) {
+      const int c = c0 + i;
       const float b = bias ? bias[c] : 0.f;
       float acc = 0.f;
       for (int j = 0; j < taps; ++j) {          // y_t = sum_j w[c][j] * u_(t - taps + 1 + j), oldest first
         const int d = taps - 1 - j;             // how far back
-        float u = 0.f;
-        if (d <= back) u = (row - (size_t)d * ld)[c] + b;
-        else if (pos - d >= 0) u = rg[(size_t)((pos - d) % taps) * C + c];
-        acc = fmaf(conv_w[(size_t)c * taps + j], u, acc);
+        float uu = 0.f;
+        if (d <= back) uu = (row - (size_t)d * ld)[c] + b;
+        else if (pos - d >= 0) uu = rg[(size_t)((pos - d) % taps) * C + c];
+        acc = fmaf(conv_w[(size_t)c * taps + j], uu, acc);
       }
-      y[c] = acc;
+      y[i] = acc;
     }
   } else {
-    for (int c = threadIdx.x; c < C; c += 128) y[c] = row[c] + (bias ? bias[c] : 0.f);
+    for (int i = threadIdx.x; i < width; i += 128) y[i] = row[c0 + i] + (bias ? bias[c0 + i] : 0.f);
   }
   __syncthreads();
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // q and k heads: one warp per head
-  for (int hh = warp; hh < g.heads + g.kv_heads; hh += 4) {
-    float* v = y + (size_t)hh * g.dim;  // q heads first, then k heads: both g.dim wide
-    if (g.unit_qk) {
-      float ss = 0.f;
-      for (int d = lane; d < g.dim; d += 32) ss = fmaf(v[d], v[d], ss);
-      ss = warp_sum(ss);
-      const float r = 1.0f / sqrtf(ss / (float)g.dim + g.eps);
-      for (int d = lane; d < g.dim; d += 32) v[d] *= r;
+  if (is_v) {
+    const int vc = c0 - nq - nk;   // first column of this head among the values
+    float* vf = v_first ? v_first + (size_t)t * nv + vc : nullptr;
+    TC* vr = v_cache + (size_t)slot * nv + vc;
+    const float lam = vmix_mode == 2 ? *vmix_lambda : 0.f;
+    for (int i = threadIdx.x; i < width; i += 128) {
+      float v = y[i];
+      if (vmix_mode == 1) vf[i] = v;
+      else if (vmix_mode == 2) v = (1.0f - lam) * v + lam * vf[i];
+      stf(vr + i, v);
     }
-    for (int p = lane; p < half; p += 32) {
-      const float a = v[2 * p], b = v[2 * p + 1];
-      v[2 * p] = a * cs[p] - b * cs[half + p];
-      v[2 * p + 1] = b * cs[p] + a * cs[half + p];
-    }
+    return;
   }
-  // values
-  if (vmix_mode != 0) {
-    float* vf = v_first + (size_t)t * nv;
-    if (vmix_mode == 1) {
-      for (int c = threadIdx.x; c < nv; c += 128) vf[c] = y[nq + nk + c];
+  float r = 1.0f;
+  if (g.unit_qk) {
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < width; i += 128) ss = fmaf(y[i], y[i], ss);
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    r = 1.0f / sqrtf((red[0] + red[1] + red[2] + red[3]) / (float)width + g.eps);
+  }
+  // pairs below rot_dims turn, the rest passes; one thread per pair (an odd last element passes alone)
+  const bool is_q = u < g.heads;
+  float* qo = q_out + (size_t)t * nq + c0;
+  TC* kr = k_cache + (size_t)slot * nk + (c0 - nq);
+  for (int p = threadIdx.x; p < (width + 1) / 2; p += 128) {
+    const bool two = 2 * p + 1 < width;
+    float a = y[2 * p] * r, b = two ? y[2 * p + 1] * r : 0.f;
+    if (p < half) {
+      const float ra = a * cs[p] - b * cs[half + p], rb = b * cs[p] + a * cs[half + p];
+      a = ra;
+      b = rb;
+    }
+    if (is_q) {
+      qo[2 * p] = a;
+      if (two) qo[2 * p + 1] = b;
     } else {
-      const float lam = *vmix_lambda;
-      for (int c = threadIdx.x; c < nv; c += 128) y[nq + nk + c] = (1.0f - lam) * y[nq + nk + c] + lam * vf[c];
+      stf(kr + 2 * p, a);
+      if (two) stf(kr + 2 * p + 1, b);
     }
   }
-  __syncthreads();
-  for (int c = threadIdx.x; c < nq; c += 128) q_out[(size_t)t * nq + c] = y[c];
-  TC* kr = k_cache + (size_t)slot * nk;
-  for (int c = threadIdx.x; c < nk; c += 128) stf(kr + c, y[nq + c]);
-  TC* vr = v_cache + (size_t)slot * nv;
-  for (int c = threadIdx.x; c < nv; c += 128) stf(vr + c, y[nq + nk + c]);
 }
 
 __global__ void __launch_bounds__(128) conv_tail_store_kernel(const float* __restrict__ proj, int ld, int C, int taps,
@@ -179,14 +194,16 @@ __global__ void __launch_bounds__(HA_WARPS * 32) heads_attention_kernel(const fl
                                                                         const TC* __restrict__ v_cache, HeadsGeom g,
                                                                         const int32_t* __restrict__ block_table, int bt_stride, int block_size,
                                                                         const PrefillTile* __restrict__ tiles, const int32_t* __restrict__ positions,
-                                                                        const int32_t* __restrict__ seq_lens, TO* __restrict__ out) {
+                                                                        const int32_t* __restrict__ seq_lens, TO* __restrict__ out, int cross_cols) {
   extern __shared__ float sm[];
   pdl_wait();
   pdl_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int a = blockIdx.y, kvh = a / (g.heads / g.kv_heads);
   const int D = g.dim, krow = g.kv_heads * g.dim, vrow = g.kv_heads * g.vdim;
-  const int VW = g.cross ? vrow : g.vdim, voff = g.cross ? 0 : kvh * g.vdim;
+  // the value columns this CTA weights: its key/value head's, or with cross a run of cross_cols columns of the whole value row
+  const int voff = g.cross ? (int)blockIdx.z * cross_cols : kvh * g.vdim;
+  const int VW = g.cross ? min(cross_cols, vrow - voff) : g.vdim;
   int t, pos, bt_row;
   bool live;
   if (DECODE) {
@@ -300,7 +317,7 @@ __global__ void __launch_bounds__(HA_WARPS * 32) heads_attention_kernel(const fl
       }
     }
   }
-  TO* orow = out + ((size_t)t * g.heads + a) * VW;
+  TO* orow = g.cross ? out + ((size_t)t * g.heads + a) * vrow + voff : out + ((size_t)t * g.heads + a) * g.vdim;
   if (!DECODE) {
     if (!live) return;
     const float inv = 1.0f / l;
@@ -618,17 +635,17 @@ int launch_attention_mma(const float* q, const bf16* k, const bf16* v, const Hea
 template <typename TC, typename TO, bool DECODE, bool VEC>
 int launch_attention_nv(int nv, dim3 grid, size_t smem, cudaStream_t s, const float* q, const TC* k, const TC* v, const HeadsGeom& g,
                         const int32_t* bt, int bt_stride, int block_size, const PrefillTile* tiles, const int32_t* positions,
-                        const int32_t* seq_lens, TO* out) {
+                        const int32_t* seq_lens, TO* out, int cross_cols) {
 #define HA_CASE(NVV)                                                                                                                   \
   if (nv <= NVV) {                                                                                                                     \
     auto kern = heads_attention_kernel<TC, TO, NVV, DECODE, VEC>;                                                                      \
     if (smem > 48 * 1024) B2_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));              \
-    B2_CUDA_OK(b2_launch(kern, grid, dim3(HA_WARPS * 32), smem, s, q, k, v, g, bt, bt_stride, block_size, tiles, positions, seq_lens, out)); \
+    B2_CUDA_OK(b2_launch(kern, grid, dim3(HA_WARPS * 32), smem, s, q, k, v, g, bt, bt_stride, block_size, tiles, positions, seq_lens, out, cross_cols)); \
     return 0;                                                                                                                          \
   }
   HA_CASE(1) HA_CASE(2) HA_CASE(4) HA_CASE(8) HA_CASE(16) HA_CASE(32)
 #undef HA_CASE
-  b2_set_error("heads_attention: %d value columns per query head exceed 1024", nv * 32);
+  b2_set_error("heads_attention: %d value columns per head exceed 1024", nv * 32);
   return -22;
 }
 
@@ -636,23 +653,29 @@ template <typename TC, typename TO>
 int launch_attention_t(const float* q, const void* k, const void* v, const HeadsGeom& g, const int32_t* bt, int bt_stride, int block_size,
                        const PrefillTile* tiles, int ntiles, const int32_t* positions, const int32_t* seq_lens, void* out, int T,
                        cudaStream_t s) {
-  const int VW = g.cross ? g.kv_heads * g.vdim : g.vdim, nv = (VW + 31) / 32;
+  // with cross a CTA takes as many whole value heads as fit 512 columns; the others go to further CTAs (blockIdx.z)
+  const int vrow = g.kv_heads * g.vdim;
+  const int cross_cols = g.cross ? g.vdim * std::max(1, std::min(g.kv_heads, 512 / std::max(g.vdim, 1))) : 0;
+  const int zs = g.cross ? (vrow + cross_cols - 1) / cross_cols : 1;
+  const int VW = g.cross ? cross_cols : g.vdim, nv = (VW + 31) / 32;
   constexpr bool can_vec = sizeof(TC) == 2;
-  const bool vec = can_vec && g.dim % 8 == 0 && VW % 64 == 0 && g.vdim % 2 == 0;
+  const bool vec = can_vec && g.dim % 8 == 0 && g.vdim % 64 == 0;
   if (tiles != nullptr) {
     const size_t smem = (size_t)HA_WARPS * g.dim * sizeof(float);
+    const dim3 grid(ntiles * 8, g.heads, zs);
     if (vec)
-      return launch_attention_nv<TC, TO, false, can_vec>(nv, dim3(ntiles * 8, g.heads), smem, s, q, (const TC*)k, (const TC*)v, g, bt, bt_stride,
-                                                         block_size, tiles, positions, seq_lens, (TO*)out);
-    return launch_attention_nv<TC, TO, false, false>(nv, dim3(ntiles * 8, g.heads), smem, s, q, (const TC*)k, (const TC*)v, g, bt, bt_stride,
-                                                     block_size, tiles, positions, seq_lens, (TO*)out);
+      return launch_attention_nv<TC, TO, false, can_vec>(nv, grid, smem, s, q, (const TC*)k, (const TC*)v, g, bt, bt_stride, block_size, tiles,
+                                                         positions, seq_lens, (TO*)out, cross_cols);
+    return launch_attention_nv<TC, TO, false, false>(nv, grid, smem, s, q, (const TC*)k, (const TC*)v, g, bt, bt_stride, block_size, tiles, positions,
+                                                     seq_lens, (TO*)out, cross_cols);
   }
   const size_t smem = ((size_t)g.dim + 2 * HA_WARPS + (size_t)HA_WARPS * VW) * sizeof(float);
+  const dim3 grid(T, g.heads, zs);
   if (vec)
-    return launch_attention_nv<TC, TO, true, can_vec>(nv, dim3(T, g.heads), smem, s, q, (const TC*)k, (const TC*)v, g, bt, bt_stride, block_size,
-                                                      nullptr, positions, seq_lens, (TO*)out);
-  return launch_attention_nv<TC, TO, true, false>(nv, dim3(T, g.heads), smem, s, q, (const TC*)k, (const TC*)v, g, bt, bt_stride, block_size,
-                                                  nullptr, positions, seq_lens, (TO*)out);
+    return launch_attention_nv<TC, TO, true, can_vec>(nv, grid, smem, s, q, (const TC*)k, (const TC*)v, g, bt, bt_stride, block_size, nullptr,
+                                                      positions, seq_lens, (TO*)out, cross_cols);
+  return launch_attention_nv<TC, TO, true, false>(nv, grid, smem, s, q, (const TC*)k, (const TC*)v, g, bt, bt_stride, block_size, nullptr, positions,
+                                                  seq_lens, (TO*)out, cross_cols);
 }
 
 }  // namespace
@@ -667,17 +690,18 @@ int launch_heads_finish(const float* proj, int ld, const HeadsGeom& g, const flo
   B2_REQUIRE(g.conv_taps == 0 || (conv_w && ring && row_seq && row_first && row_end), "heads_finish: the convolution needs its weights and state");
   B2_REQUIRE(vmix_mode == 0 || v_first != nullptr, "heads_finish: value mixing needs the first layer's values");
   const int C = g.heads * g.dim + g.kv_heads * (g.dim + g.vdim);
-  const size_t smem = ((size_t)C + std::max(g.rot_dims, 2)) * sizeof(float);
-  B2_REQUIRE(smem <= 200 * 1024, "heads_finish: q | k | v row of %d numbers exceeds shared memory", C);
+  const size_t smem = ((size_t)std::max(g.dim, g.vdim) + std::max(g.rot_dims, 2)) * sizeof(float);
+  B2_REQUIRE(smem <= 200 * 1024, "heads_finish: a head of %d numbers exceeds shared memory", std::max(g.dim, g.vdim));
+  const dim3 fgrid(T, g.heads + 2 * g.kv_heads);
   if (cache_f32) {
     auto kern = heads_finish_kernel<float>;
     if (smem > 48 * 1024) B2_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    B2_CUDA_OK(b2_launch(kern, dim3(T), dim3(128), smem, s, proj, ld, g, bias, conv_w, (const float*)ring, row_seq, row_first, positions, slots,
+    B2_CUDA_OK(b2_launch(kern, fgrid, dim3(128), smem, s, proj, ld, g, bias, conv_w, (const float*)ring, row_seq, row_first, positions, slots,
                          vmix_mode, vmix_lambda, v_first, q_out, (float*)k_cache, (float*)v_cache));
   } else {
     auto kern = heads_finish_kernel<bf16>;
     if (smem > 48 * 1024) B2_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    B2_CUDA_OK(b2_launch(kern, dim3(T), dim3(128), smem, s, proj, ld, g, bias, conv_w, (const float*)ring, row_seq, row_first, positions, slots,
+    B2_CUDA_OK(b2_launch(kern, fgrid, dim3(128), smem, s, proj, ld, g, bias, conv_w, (const float*)ring, row_seq, row_first, positions, slots,
                          vmix_mode, vmix_lambda, v_first, q_out, (bf16*)k_cache, (bf16*)v_cache));
   }
   if (g.conv_taps > 1)

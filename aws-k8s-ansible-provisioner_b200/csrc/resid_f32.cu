@@ -121,7 +121,7 @@ __global__ void __launch_bounds__(128) embed_scaled_kernel(const int32_t* __rest
   for (int i = threadIdx.x; i < W; i += 128) h[(size_t)t * W + i] = (float)row[i] * scale;
 }
 
-// One CTA per token, one warp per piece (pieces round robin over the four warps).  ADD: h += norm(y + bias) * gain, and when
+// One warp per piece; a token's pieces are spread over the warps of one CTA, or of several when the step has few tokens.  ADD: h += norm(y + bias) * gain, and when
 // gain_next is given the norm in front of the next sublayer follows at once, x = norm(h) * gain_next (the pieces of both
 // norms are the same, so the warp that updated a piece normalises it).
 template <typename TX, bool ADD>
@@ -134,7 +134,8 @@ __global__ void __launch_bounds__(128) group_norm_kernel(const float* __restrict
   const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int piece = W / groups;
   const float* row = src + (size_t)(rows ? rows[t] : t) * W;
-  for (int gi = warp; gi < groups; gi += 4) {
+  // pieces round robin over the warps of the token's CTAs (gridDim.y CTAs of four warps: few tokens get more CTAs each)
+  for (int gi = blockIdx.y * 4 + warp; gi < groups; gi += 4 * gridDim.y) {
     const int o = gi * piece;
     float ss = 0.f;
     for (int i = lane; i < piece; i += 32) {
@@ -168,7 +169,7 @@ __global__ void __launch_bounds__(256) clamped_gate_kernel(const float* __restri
   pdl_launch_dependents();
   const int t = blockIdx.x;
   const float* row = gu + (size_t)t * 2 * F;
-  for (int i = threadIdx.x; i < F; i += 256) {
+  for (int i = blockIdx.y * 256 + threadIdx.x; i < F; i += 256 * gridDim.y) {
     const float g = fminf(row[i], limit);
     const float u = fminf(fmaxf(row[F + i], -limit), limit);
     act[(size_t)t * F + i] = (TX)(g / (1.0f + expf(-sharp * g)) * (u + 1.0f));
@@ -176,6 +177,8 @@ __global__ void __launch_bounds__(256) clamped_gate_kernel(const float* __restri
 }
 
 }  // namespace
+
+static dim3 gn_grid(int T, int groups) { return dim3(T, T >= 1024 ? 1 : std::max(1, (groups + 3) / 4)); }
 
 int launch_embed_scaled(const int32_t* ids, const void* table, int table_f32, float scale, float* h, int T, int W, int vocab, cudaStream_t s) {
   if (T <= 0) return 0;
@@ -189,10 +192,10 @@ int launch_group_norm(const float* h, const float* gain, void* x, int x_f32, int
   if (T <= 0) return 0;
   B2_REQUIRE(groups >= 1 && W % groups == 0, "group_norm: width %d is not %d equal pieces", W, groups);
   if (x_f32)
-    B2_CUDA_OK(b2_launch(group_norm_kernel<float, false>, dim3(T), dim3(128), 0, s, h, (const float*)nullptr, gain, (float*)x, (float*)nullptr, W, groups, eps, rows,
+    B2_CUDA_OK(b2_launch(group_norm_kernel<float, false>, gn_grid(T, groups), dim3(128), 0, s, h, (const float*)nullptr, gain, (float*)x, (float*)nullptr, W, groups, eps, rows,
                          (const float*)nullptr));
   else
-    B2_CUDA_OK(b2_launch(group_norm_kernel<bf16, false>, dim3(T), dim3(128), 0, s, h, (const float*)nullptr, gain, (bf16*)x, (float*)nullptr, W, groups, eps, rows,
+    B2_CUDA_OK(b2_launch(group_norm_kernel<bf16, false>, gn_grid(T, groups), dim3(128), 0, s, h, (const float*)nullptr, gain, (bf16*)x, (float*)nullptr, W, groups, eps, rows,
                          (const float*)nullptr));
   return 0;
 }
@@ -203,16 +206,17 @@ int launch_group_norm_add(float* h, const float* y, const float* bias, const flo
   B2_REQUIRE(groups >= 1 && W % groups == 0, "group_norm: width %d is not %d equal pieces", W, groups);
   B2_REQUIRE((gain_next == nullptr) == (x_next == nullptr), "group_norm_add: the following norm needs its gain and its output");
   if (x_f32 || x_next == nullptr)
-    B2_CUDA_OK(b2_launch(group_norm_kernel<float, true>, dim3(T), dim3(128), 0, s, y, bias, gain, (float*)x_next, h, W, groups, eps, (const int32_t*)nullptr, gain_next));
+    B2_CUDA_OK(b2_launch(group_norm_kernel<float, true>, gn_grid(T, groups), dim3(128), 0, s, y, bias, gain, (float*)x_next, h, W, groups, eps, (const int32_t*)nullptr, gain_next));
   else
-    B2_CUDA_OK(b2_launch(group_norm_kernel<bf16, true>, dim3(T), dim3(128), 0, s, y, bias, gain, (bf16*)x_next, h, W, groups, eps, (const int32_t*)nullptr, gain_next));
+    B2_CUDA_OK(b2_launch(group_norm_kernel<bf16, true>, gn_grid(T, groups), dim3(128), 0, s, y, bias, gain, (bf16*)x_next, h, W, groups, eps, (const int32_t*)nullptr, gain_next));
   return 0;
 }
 
 int launch_clamped_gate(const float* gu, void* act, int act_f32, int T, int F, float limit, float sharp, cudaStream_t s) {
   if (T <= 0) return 0;
-  if (act_f32) B2_CUDA_OK(b2_launch(clamped_gate_kernel<float>, dim3(T), dim3(256), 0, s, gu, (float*)act, F, limit, sharp));
-  else B2_CUDA_OK(b2_launch(clamped_gate_kernel<bf16>, dim3(T), dim3(256), 0, s, gu, (bf16*)act, F, limit, sharp));
+  const dim3 grid(T, T >= 1024 ? 1 : std::max(1, std::min((F + 255) / 256, 1024 / T)));   // few tokens: several CTAs per row
+  if (act_f32) B2_CUDA_OK(b2_launch(clamped_gate_kernel<float>, grid, dim3(256), 0, s, gu, (float*)act, F, limit, sharp));
+  else B2_CUDA_OK(b2_launch(clamped_gate_kernel<bf16>, grid, dim3(256), 0, s, gu, (bf16*)act, F, limit, sharp));
   return 0;
 }
 

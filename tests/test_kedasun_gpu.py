@@ -126,6 +126,7 @@ SINGLE = {
     "window without kept tokens": [(att2(2, 1, 8, 8, 2.5, 2, window=17, keep=0), None)],
     "kept tokens beyond the window's reach": [(att2(2, 2, 8, 8, 2.5, 6, window=3, keep=40), None)],
     "one tap": [(att2(2, 2, 8, 8, 1.0, 1, window=6, keep=1), None)],
+    "a value row wider than one pass over it": [(att2(12, 12, 8, 64, 1.0, 2, window=20, keep=3), None)],
 }
 
 
