@@ -57,92 +57,98 @@ __device__ __forceinline__ void pair_cos_sin(int pos, int i, int dims, float bas
   *s = (float)sd;
 }
 
-// One CTA per (token, head): blockIdx.y names a query head, then a key head, then a value head.
-// proj [T][ld] fp32: q (heads * dim) | k (kv_heads * dim) | v (kv_heads * vdim) | anything else.
+// A CTA takes `upc` heads of one token, counted through the query heads, then the key heads, then the value heads, one warp per
+// head at a time: all of them for prompt-sized steps (the token's cosines and sines are formed once), four when the step has few
+// tokens.  proj [T][ld] fp32: q (heads * dim) | k (kv_heads * dim) | v (kv_heads * vdim) | anything else.
 template <typename TC>
 __global__ void __launch_bounds__(128) heads_finish_kernel(const float* __restrict__ proj, int ld, HeadsGeom g, const float* __restrict__ bias,
                                                            const float* __restrict__ conv_w, const float* __restrict__ ring,
                                                            const int32_t* __restrict__ row_seq, const int32_t* __restrict__ row_first,
                                                            const int32_t* __restrict__ positions, const int32_t* __restrict__ slots,
                                                            int vmix_mode, const float* __restrict__ vmix_lambda, float* __restrict__ v_first,
-                                                           float* __restrict__ q_out, TC* __restrict__ k_cache, TC* __restrict__ v_cache) {
+                                                           float* __restrict__ q_out, TC* __restrict__ k_cache, TC* __restrict__ v_cache, int upc) {
   extern __shared__ float sm[];
-  __shared__ float red[4];
   pdl_wait();
   pdl_launch_dependents();
-  const int t = blockIdx.x, u = blockIdx.y;
+  const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int slot = slots[t];
   if (slot < 0) return;  // padding row of a decode bucket
   const int pos = positions[t];
   const int nq = g.heads * g.dim, nk = g.kv_heads * g.dim, nv = g.kv_heads * g.vdim, C = nq + nk + nv;
-  const bool is_v = u >= g.heads + g.kv_heads;
-  const int width = is_v ? g.vdim : g.dim;
-  const int c0 = is_v ? nq + nk + (u - g.heads - g.kv_heads) * g.vdim : u * g.dim;   // first channel of this head in q | k | v
-  float* y = sm;              // [width] the head after bias and convolution
-  float* cs = sm + width;     // [rot_dims] cos | sin
-  const int half = is_v ? 0 : g.rot_dims / 2;
-  for (int i = threadIdx.x; i < half; i += 128) pair_cos_sin(pos, i, g.rot_dims, g.rot_base, &cs[i], &cs[half + i]);
-  const float* row = proj + (size_t)t * ld;
-  if (g.conv_taps > 0) {
-    const int taps = g.conv_taps, back = t - row_first[t];
-    const float* rg = ring + (size_t)row_seq[t] * taps * C;
-    for (int i = threadIdx.x; i < width; i += 128) {
-      const int c = c0 + i;
-      const float b = bias ? bias[c] : 0.f;
-      float acc = 0.f;
-      for (int j = 0; j < taps; ++j) {          // y_t = sum_j w[c][j] * u_(t - taps + 1 + j), oldest first
-        const int d = taps - 1 - j;             // how far back
-        float uu = 0.f;
-        if (d <= back) uu = (row - (size_t)d * ld)[c] + b;
-        else if (pos - d >= 0) uu = rg[(size_t)((pos - d) % taps) * C + c];
-        acc = fmaf(conv_w[(size_t)c * taps + j], uu, acc);
-      }
-      y[i] = acc;
-    }
-  } else {
-    for (int i = threadIdx.x; i < width; i += 128) y[i] = row[c0 + i] + (bias ? bias[c0 + i] : 0.f);
-  }
+  const int units = g.heads + 2 * g.kv_heads, u_lo = blockIdx.y * upc, u_hi = min(units, u_lo + upc);
+  const int maxw = max(g.dim, g.vdim);
+  float* y = sm + (size_t)warp * maxw;      // this warp's head after bias and convolution
+  float* cs = sm + (size_t)4 * maxw;        // [rot_dims] cos | sin
+  const int rhalf = g.rot_dims / 2;
+  if (u_lo < g.heads + g.kv_heads)
+    for (int i = threadIdx.x; i < rhalf; i += 128) pair_cos_sin(pos, i, g.rot_dims, g.rot_base, &cs[i], &cs[rhalf + i]);
   __syncthreads();
-  if (is_v) {
-    const int vc = c0 - nq - nk;   // first column of this head among the values
-    float* vf = v_first ? v_first + (size_t)t * nv + vc : nullptr;
-    TC* vr = v_cache + (size_t)slot * nv + vc;
-    const float lam = vmix_mode == 2 ? *vmix_lambda : 0.f;
-    for (int i = threadIdx.x; i < width; i += 128) {
-      float v = y[i];
-      if (vmix_mode == 1) vf[i] = v;
-      else if (vmix_mode == 2) v = (1.0f - lam) * v + lam * vf[i];
-      stf(vr + i, v);
-    }
-    return;
-  }
-  float r = 1.0f;
-  if (g.unit_qk) {
-    float ss = 0.f;
-    for (int i = threadIdx.x; i < width; i += 128) ss = fmaf(y[i], y[i], ss);
-    ss = warp_sum(ss);
-    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
-    __syncthreads();
-    r = 1.0f / sqrtf((red[0] + red[1] + red[2] + red[3]) / (float)width + g.eps);
-  }
-  // pairs below rot_dims turn, the rest passes; one thread per pair (an odd last element passes alone)
-  const bool is_q = u < g.heads;
-  float* qo = q_out + (size_t)t * nq + c0;
-  TC* kr = k_cache + (size_t)slot * nk + (c0 - nq);
-  for (int p = threadIdx.x; p < (width + 1) / 2; p += 128) {
-    const bool two = 2 * p + 1 < width;
-    float a = y[2 * p] * r, b = two ? y[2 * p + 1] * r : 0.f;
-    if (p < half) {
-      const float ra = a * cs[p] - b * cs[half + p], rb = b * cs[p] + a * cs[half + p];
-      a = ra;
-      b = rb;
-    }
-    if (is_q) {
-      qo[2 * p] = a;
-      if (two) qo[2 * p + 1] = b;
+  const float* row = proj + (size_t)t * ld;
+  for (int u = u_lo + warp; u < u_hi; u += 4) {
+    const bool is_v = u >= g.heads + g.kv_heads;
+    const int width = is_v ? g.vdim : g.dim;
+    const int c0 = is_v ? nq + nk + (u - g.heads - g.kv_heads) * g.vdim : u * g.dim;   // first channel of this head in q | k | v
+    const int half = is_v ? 0 : rhalf;
+    __syncwarp();   // the head before this one is out of y
+    if (g.conv_taps > 0) {
+      const int taps = g.conv_taps, back = t - row_first[t];
+      const float* rg = ring + (size_t)row_seq[t] * taps * C;
+      for (int i = lane; i < width; i += 32) {
+        const int c = c0 + i;
+        const float b = bias ? bias[c] : 0.f;
+        float acc = 0.f;
+        for (int j = 0; j < taps; ++j) {          // y_t = sum_j w[c][j] * u_(t - taps + 1 + j), oldest first
+          const int d = taps - 1 - j;             // how far back
+          float uu = 0.f;
+          if (d <= back) uu = (row - (size_t)d * ld)[c] + b;
+          else if (pos - d >= 0) uu = rg[(size_t)((pos - d) % taps) * C + c];
+          acc = fmaf(conv_w[(size_t)c * taps + j], uu, acc);
+        }
+        y[i] = acc;
+      }
     } else {
-      stf(kr + 2 * p, a);
-      if (two) stf(kr + 2 * p + 1, b);
+      for (int i = lane; i < width; i += 32) y[i] = row[c0 + i] + (bias ? bias[c0 + i] : 0.f);
+    }
+    __syncwarp();
+    if (is_v) {
+      const int vc = c0 - nq - nk;   // first column of this head among the values
+      float* vf = v_first ? v_first + (size_t)t * nv + vc : nullptr;
+      TC* vr = v_cache + (size_t)slot * nv + vc;
+      const float lam = vmix_mode == 2 ? *vmix_lambda : 0.f;
+      for (int i = lane; i < width; i += 32) {
+        float v = y[i];
+        if (vmix_mode == 1) vf[i] = v;
+        else if (vmix_mode == 2) v = (1.0f - lam) * v + lam * vf[i];
+        stf(vr + i, v);
+      }
+      continue;
+    }
+    float r = 1.0f;
+    if (g.unit_qk) {
+      float ss = 0.f;
+      for (int i = lane; i < width; i += 32) ss = fmaf(y[i], y[i], ss);
+      ss = warp_sum(ss);
+      r = 1.0f / sqrtf(ss / (float)width + g.eps);
+    }
+    // pairs below rot_dims turn, the rest passes; one lane per pair (an odd last element passes alone)
+    const bool is_q = u < g.heads;
+    float* qo = q_out + (size_t)t * nq + c0;
+    TC* kr = k_cache + (size_t)slot * nk + (c0 - nq);
+    for (int p = lane; p < (width + 1) / 2; p += 32) {
+      const bool two = 2 * p + 1 < width;
+      float a = y[2 * p] * r, b = two ? y[2 * p + 1] * r : 0.f;
+      if (p < half) {
+        const float ra = a * cs[p] - b * cs[half + p], rb = b * cs[p] + a * cs[half + p];
+        a = ra;
+        b = rb;
+      }
+      if (is_q) {
+        qo[2 * p] = a;
+        if (two) qo[2 * p + 1] = b;
+      } else {
+        stf(kr + 2 * p, a);
+        if (two) stf(kr + 2 * p + 1, b);
+      }
     }
   }
 }
@@ -492,15 +498,18 @@ __global__ void __launch_bounds__(128 * HPC) heads_attention_mma_kernel(const fl
     __syncthreads();
     float sc[HM_KEYS / 8][4];
 #pragma unroll
-    for (int n = 0; n < HM_KEYS / 8; ++n) {
-      sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.f;
-      const uint32_t kb = smem_u32(Kt + (n * 8 + (lane & 7)) * QS + (lane >> 3) * 8);   // four 8 x 8 blocks: two k-steps of one key group
+    for (int n = 0; n < HM_KEYS / 8; ++n) sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.f;
+    {
+      const uint32_t kb = smem_u32(Kt + (lane & 7) * QS + (lane >> 3) * 8);   // four 8 x 8 blocks: two k-steps of one key group
 #pragma unroll
-      for (int kk = 0; kk < KD; kk += 2) {
-        uint32_t kf[4];
-        ldmatrix_x4(kf, kb + kk * 16 * 2);
-        mma_bf16_16816(sc[n], qa[kk], kf[0], kf[1]);
-        mma_bf16_16816(sc[n], qa[kk + 1], kf[2], kf[3]);
+      for (int kk = 0; kk < KD; kk += 2) {       // k-steps outside, key groups inside: neighbouring MMAs feed different accumulators
+#pragma unroll
+        for (int n = 0; n < HM_KEYS / 8; ++n) {
+          uint32_t kf[4];
+          ldmatrix_x4(kf, kb + (n * 8 * QS + kk * 16) * 2);
+          mma_bf16_16816(sc[n], qa[kk], kf[0], kf[1]);
+          mma_bf16_16816(sc[n], qa[kk + 1], kf[2], kf[3]);
+        }
       }
     }
     // scale, distance penalty, mask; row maxima over the quad.  A tile that every row of the CTA sees whole needs no mask.
@@ -690,19 +699,20 @@ int launch_heads_finish(const float* proj, int ld, const HeadsGeom& g, const flo
   B2_REQUIRE(g.conv_taps == 0 || (conv_w && ring && row_seq && row_first && row_end), "heads_finish: the convolution needs its weights and state");
   B2_REQUIRE(vmix_mode == 0 || v_first != nullptr, "heads_finish: value mixing needs the first layer's values");
   const int C = g.heads * g.dim + g.kv_heads * (g.dim + g.vdim);
-  const size_t smem = ((size_t)std::max(g.dim, g.vdim) + std::max(g.rot_dims, 2)) * sizeof(float);
+  const size_t smem = ((size_t)4 * std::max(g.dim, g.vdim) + std::max(g.rot_dims, 2)) * sizeof(float);
   B2_REQUIRE(smem <= 200 * 1024, "heads_finish: a head of %d numbers exceeds shared memory", std::max(g.dim, g.vdim));
-  const dim3 fgrid(T, g.heads + 2 * g.kv_heads);
+  const int units = g.heads + 2 * g.kv_heads, upc = T >= 256 ? units : 4;   // prompt-sized steps: a CTA per token
+  const dim3 fgrid(T, (units + upc - 1) / upc);
   if (cache_f32) {
     auto kern = heads_finish_kernel<float>;
     if (smem > 48 * 1024) B2_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     B2_CUDA_OK(b2_launch(kern, fgrid, dim3(128), smem, s, proj, ld, g, bias, conv_w, (const float*)ring, row_seq, row_first, positions, slots,
-                         vmix_mode, vmix_lambda, v_first, q_out, (float*)k_cache, (float*)v_cache));
+                         vmix_mode, vmix_lambda, v_first, q_out, (float*)k_cache, (float*)v_cache, upc));
   } else {
     auto kern = heads_finish_kernel<bf16>;
     if (smem > 48 * 1024) B2_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     B2_CUDA_OK(b2_launch(kern, fgrid, dim3(128), smem, s, proj, ld, g, bias, conv_w, (const float*)ring, row_seq, row_first, positions, slots,
-                         vmix_mode, vmix_lambda, v_first, q_out, (bf16*)k_cache, (bf16*)v_cache));
+                         vmix_mode, vmix_lambda, v_first, q_out, (bf16*)k_cache, (bf16*)v_cache, upc));
   }
   if (g.conv_taps > 1)
     B2_CUDA_OK(b2_launch(conv_tail_store_kernel, dim3(T), dim3(128), 0, s, proj, ld, C, g.conv_taps, bias, ring, row_seq, row_end, positions, slots));
