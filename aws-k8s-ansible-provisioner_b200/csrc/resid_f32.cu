@@ -124,6 +124,7 @@ __global__ void __launch_bounds__(128) embed_scaled_kernel(const int32_t* __rest
 // One warp per piece; a token's pieces are spread over the warps of one CTA, or of several when the step has few tokens.  ADD: h += norm(y + bias) * gain, and when
 // gain_next is given the norm in front of the next sublayer follows at once, x = norm(h) * gain_next (the pieces of both
 // norms are the same, so the warp that updated a piece normalises it).
+constexpr int GN_REG = 16;   // values of a piece a lane keeps in registers (pieces up to 512 wide)
 template <typename TX, bool ADD>
 __global__ void __launch_bounds__(128) group_norm_kernel(const float* __restrict__ src, const float* __restrict__ bias,
                                                          const float* __restrict__ gain, TX* __restrict__ x, float* __restrict__ h, int W,
@@ -137,6 +138,43 @@ __global__ void __launch_bounds__(128) group_norm_kernel(const float* __restrict
   // pieces round robin over the warps of the token's CTAs (gridDim.y CTAs of four warps: few tokens get more CTAs each)
   for (int gi = blockIdx.y * 4 + warp; gi < groups; gi += 4 * gridDim.y) {
     const int o = gi * piece;
+    if (piece <= 32 * GN_REG) {
+      // the piece fits the warp's registers: every load of a pass is in flight at once, and nothing is read twice
+      float v[GN_REG], ss = 0.f;
+#pragma unroll
+      for (int k = 0; k < GN_REG; ++k) {
+        const int i = lane + 32 * k;
+        v[k] = i < piece ? row[o + i] + (bias ? bias[o + i] : 0.f) : 0.f;
+        ss = fmaf(v[k], v[k], ss);
+      }
+      ss = warp_sum(ss);
+      const float r = 1.0f / sqrtf(ss / (float)piece + eps);
+      float ss2 = 0.f;
+#pragma unroll
+      for (int k = 0; k < GN_REG; ++k) {
+        const int i = lane + 32 * k;
+        if (i < piece) {
+          v[k] = v[k] * r * gain[o + i];
+          if (ADD) {
+            v[k] += h[(size_t)t * W + o + i];
+            h[(size_t)t * W + o + i] = v[k];
+            ss2 = fmaf(v[k], v[k], ss2);
+          } else {
+            x[(size_t)t * W + o + i] = (TX)v[k];
+          }
+        }
+      }
+      if (ADD && gain_next != nullptr) {
+        ss2 = warp_sum(ss2);
+        const float r2 = 1.0f / sqrtf(ss2 / (float)piece + eps);
+#pragma unroll
+        for (int k = 0; k < GN_REG; ++k) {
+          const int i = lane + 32 * k;
+          if (i < piece) x[(size_t)t * W + o + i] = (TX)(v[k] * r2 * gain_next[o + i]);
+        }
+      }
+      continue;
+    }
     float ss = 0.f;
     for (int i = lane; i < piece; i += 32) {
       const float v = row[o + i] + (bias ? bias[o + i] : 0.f);

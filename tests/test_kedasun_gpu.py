@@ -147,6 +147,22 @@ def test_each_mechanism_alone(name):
             assert err(e.get_logits(1)[0], ref[p]) < F32_BAR, "decoded position %d" % p
 
 
+def test_norm_pieces_wider_than_a_warp_keeps():
+    """One piece of 576 numbers (more than the 512 a warp holds in registers) beside a model whose pieces are 36 wide."""
+    for groups in (1, 16):
+        cfg = model([(att(2, 1, 8, 8, 0.3, rot=4), ff(40)), (att2(2, 2, 8, 8, 1.1, 3, window=9, keep=2, v_mix=False), ff(24))], vocab=53, width=576, groups=groups)
+        w = random_weights(cfg, seed=80)
+        toks = tokens(cfg, 30, 81)
+        ref = ref_logits(cfg, w, toks)
+        with engine(cfg, w) as e:
+            sid = e.seq_create(32)
+            lg, _ = e.prefill_logits([sid], [toks[:27]], list(range(27)))
+            assert err(lg, ref[:27]) < F32_BAR
+            for p in range(27, 30):
+                e.decode_step([sid], in_tokens=[toks[p]], want_output=False)
+                assert err(e.get_logits(1)[0], ref[p]) < F32_BAR
+
+
 @pytest.mark.parametrize("make", [cfg_a, cfg_b])
 def test_bf16_close_to_the_restatement(make):
     cfg = make()
