@@ -407,7 +407,7 @@ __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t* r, uint32_t addr) {
 
 // HPC query heads of one key/value head per CTA (four warps each) share the staged key and value tiles.
 template <int KD, int NO, int HPC, typename TO>
-__global__ void __launch_bounds__(128 * HPC) heads_attention_mma_kernel(const float* __restrict__ q, const bf16* __restrict__ k_cache,
+__global__ void __launch_bounds__(128 * HPC, 2) heads_attention_mma_kernel(const float* __restrict__ q, const bf16* __restrict__ k_cache,
                                                                   const bf16* __restrict__ v_cache, HeadsGeom g,
                                                                   const int32_t* __restrict__ block_table, int bt_stride, int block_size,
                                                                   const PrefillTile* __restrict__ tiles, TO* __restrict__ out) {
@@ -435,17 +435,8 @@ __global__ void __launch_bounds__(128 * HPC) heads_attention_mma_kernel(const fl
     *reinterpret_cast<uint2*>(Qs + hr * QS + c4) = pk;
   }
   __syncthreads();
-  uint32_t qa[KD][4];
-  {
-    const bf16* q0 = Qs + (hl * HM_ROWS + warp * 16 + gq) * QS + 2 * tq;
-#pragma unroll
-    for (int kk = 0; kk < KD; ++kk) {
-      qa[kk][0] = *reinterpret_cast<const uint32_t*>(q0 + kk * 16);
-      qa[kk][1] = *reinterpret_cast<const uint32_t*>(q0 + 8 * QS + kk * 16);
-      qa[kk][2] = *reinterpret_cast<const uint32_t*>(q0 + kk * 16 + 8);
-      qa[kk][3] = *reinterpret_cast<const uint32_t*>(q0 + 8 * QS + kk * 16 + 8);
-    }
-  }
+  // the query fragments stay in shared memory and are read again for every key tile (32 registers less per thread)
+  const uint32_t qbase = smem_u32(Qs + (hl * HM_ROWS + warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * QS + (lane >> 4) * 8);
   const float slope = g.slopes ? (float)exp2(-(double)g.slope_exp * (double)(a + 1) / (double)g.heads) : 0.f;
   const int r0 = warp * 16 + gq, r1 = r0 + 8;                 // this thread's two query rows
   const int p0 = tl.q_pos0 + r0, p1 = tl.q_pos0 + r1;
@@ -503,12 +494,15 @@ __global__ void __launch_bounds__(128 * HPC) heads_attention_mma_kernel(const fl
       const uint32_t kb = smem_u32(Kt + (lane & 7) * QS + (lane >> 3) * 8);   // four 8 x 8 blocks: two k-steps of one key group
 #pragma unroll
       for (int kk = 0; kk < KD; kk += 2) {       // k-steps outside, key groups inside: neighbouring MMAs feed different accumulators
+        uint32_t qa0[4], qa1[4];
+        ldmatrix_x4(qa0, qbase + kk * 16 * 2);
+        ldmatrix_x4(qa1, qbase + (kk + 1) * 16 * 2);
 #pragma unroll
         for (int n = 0; n < HM_KEYS / 8; ++n) {
           uint32_t kf[4];
           ldmatrix_x4(kf, kb + (n * 8 * QS + kk * 16) * 2);
-          mma_bf16_16816(sc[n], qa[kk], kf[0], kf[1]);
-          mma_bf16_16816(sc[n], qa[kk + 1], kf[2], kf[3]);
+          mma_bf16_16816(sc[n], qa0, kf[0], kf[1]);
+          mma_bf16_16816(sc[n], qa1, kf[2], kf[3]);
         }
       }
     }
