@@ -1623,7 +1623,7 @@ int list_tensor_count(const b2_engine* e) {
   if (e->cfg.arch == B2_ARCH_KEDASUN) {
     int n = 3;  // embed, head, final.norm
     for (const ListLayer& L : e->ll) {
-      n += 2 + 5;                                               // norm1, norm1b; q, k, v, o, vmix
+      n += 2 + 4;                                               // norm1, norm1b; q, k, v, o (vmix is counted apart: only a blending layer needs it)
       if (L.sp.mixer == B2_MIXER_CONV_ATTENTION) n += 4 + 3 + 2;  // biases of q, k, v, o; their convolutions; talk, g
       if (L.sp.ff == B2_FF_CLAMPED_GATED) n += 2 + 3;           // norm2, norm2b; gate, up, down
     }
@@ -2485,7 +2485,12 @@ extern "C" int b2_engine_finalize(b2_engine* e) {
   const int arch = e->cfg.arch;
   if (list_arch(arch)) {
     const int want = list_tensor_count(e);
-    B2_REQUIRE((int)e->loaded.size() == want, "weights incomplete: %d of %d tensors loaded", (int)e->loaded.size(), want);
+    int have = 0;
+    for (auto& kv : e->loaded)
+      if (kv.first.size() < 9 || kv.first.compare(kv.first.size() - 9, 9, ".mix.vmix") != 0) ++have;
+    for (size_t l = 0; l < e->ll.size(); ++l)   // the blend weight: needed by the layers that blend, harmless elsewhere
+      B2_REQUIRE(e->ll[l].vmix_mode != 2 || e->loaded.count("l" + std::to_string(l) + ".mix.vmix"), "weights incomplete: l%zu.mix.vmix missing", l);
+    B2_REQUIRE(have == want, "weights incomplete: %d of %d tensors loaded", have, want);
     e->finalized = true;
     return 0;
   }

@@ -365,6 +365,21 @@ def test_a_sequence_cut_back_to_nothing_starts_over():
         assert err(lg, ref) < F32_BAR
 
 
+def test_blend_weight_is_needed_only_where_values_are_blended():
+    cfg = cfg_a()     # layer 0 supplies the first values, layers 1 and 3 blend, layer 2 stays out
+    w = random_weights(cfg, seed=45)
+    toks = tokens(cfg, 20, 46)
+    ref = ref_logits(cfg, w, toks)
+    P = pkg()
+    lean = {k: v for k, v in w.items() if k not in ("l0.mix.vmix", "l2.mix.vmix")}
+    with engine(cfg, lean) as e:
+        sid = e.seq_create(32)
+        lg, _ = e.prefill_logits([sid], [toks], list(range(20)))
+        assert err(lg, ref) < F32_BAR
+    with pytest.raises(P.B2Error):
+        engine(cfg, {k: v for k, v in w.items() if k != "l3.mix.vmix"})
+
+
 def test_greedy_generation_through_the_engine():
     cfg = cfg_a()
     w = random_weights(cfg, seed=19)
