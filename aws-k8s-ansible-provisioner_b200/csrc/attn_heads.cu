@@ -373,7 +373,7 @@ __global__ void __launch_bounds__(128) talk_gate_kernel(const float* __restrict_
   pdl_launch_dependents();
   const int t = blockIdx.x, rep = heads / kv_heads, vrow = kv_heads * vdim;
   const float* cr = cross + (size_t)t * heads * vrow;
-  for (int i = threadIdx.x; i < heads * vdim; i += 128) {
+  for (int i = blockIdx.y * 128 + threadIdx.x; i < heads * vdim; i += 128 * gridDim.y) {
     const int a = i / vdim, d = i - a * vdim, col = (a / rep) * vdim + d;
     float o = 0.f;
     for (int b = 0; b < heads; ++b) o = fmaf(talk[a * heads + b], cr[(size_t)b * vrow + col], o);
@@ -465,13 +465,13 @@ __global__ void __launch_bounds__(128 * HPC, 2) heads_attention_mma_kernel(const
       const int r = i / (D / 8), c8 = (i - r * (D / 8)) * 8, j = key0 + r;
       const bool in = j <= last_key;
       const bf16* src = k_cache + ((size_t)(in ? bt[j / block_size] : 0) * block_size + j % block_size) * krow + (size_t)kvh * D + c8;
-      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(kd + r * QS + c8)), "l"(src), "r"(in ? 16 : 0) : "memory");
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(kd + r * QS + c8)), "l"(src), "r"(in ? 16 : 0));   // ordered by the commit / wait below, which do clobber memory
     }
     for (int i = threadIdx.x; i < HM_KEYS * (DV / 8); i += NT) {
       const int r = i / (DV / 8), c8 = (i - r * (DV / 8)) * 8, j = key0 + r;
       const bool in = j <= last_key;
       const bf16* src = v_cache + ((size_t)(in ? bt[j / block_size] : 0) * block_size + j % block_size) * vrow + (size_t)vh * DV + c8;
-      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(vd + r * VS + c8)), "l"(src), "r"(in ? 16 : 0) : "memory");
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(vd + r * VS + c8)), "l"(src), "r"(in ? 16 : 0));   // ordered by the commit / wait below, which do clobber memory
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
@@ -739,8 +739,9 @@ int launch_heads_attention(const float* q, const void* k_cache, const void* v_ca
 int launch_talk_gate(const float* cross, const float* talk, const float* gate, int gate_ld, void* out, int out_f32, int heads, int kv_heads,
                      int vdim, int T, cudaStream_t s) {
   if (T <= 0) return 0;
-  if (out_f32) B2_CUDA_OK(b2_launch(talk_gate_kernel<float>, dim3(T), dim3(128), 0, s, cross, talk, gate, gate_ld, (float*)out, heads, kv_heads, vdim));
-  else B2_CUDA_OK(b2_launch(talk_gate_kernel<bf16>, dim3(T), dim3(128), 0, s, cross, talk, gate, gate_ld, (bf16*)out, heads, kv_heads, vdim));
+  const dim3 grid(T, T >= 1024 ? 1 : std::max(1, std::min((heads * vdim + 127) / 128, 1024 / T)));   // few tokens: several CTAs per row
+  if (out_f32) B2_CUDA_OK(b2_launch(talk_gate_kernel<float>, grid, dim3(128), 0, s, cross, talk, gate, gate_ld, (float*)out, heads, kv_heads, vdim));
+  else B2_CUDA_OK(b2_launch(talk_gate_kernel<bf16>, grid, dim3(128), 0, s, cross, talk, gate, gate_ld, (bf16*)out, heads, kv_heads, vdim));
   return 0;
 }
 
