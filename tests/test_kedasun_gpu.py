@@ -380,6 +380,70 @@ def test_blend_weight_is_needed_only_where_values_are_blended():
         engine(cfg, {k: v for k, v in w.items() if k != "l3.mix.vmix"})
 
 
+MMA_SIZES = [(32, 32), (64, 32), (64, 64), (96, 64), (96, 96), (128, 64), (128, 128), (192, 128), (256, 128)]
+
+
+def random_model(seed):
+    """A random layer list: head counts, sizes (among them every pair the tensor-core prompt kernel is built for), windows, kept
+    tokens, taps, rotated dims, norm pieces, layer order, value mixing and feed-forwards all drawn from the seed."""
+    import random
+    r = random.Random(seed)
+    kv = r.choice([1, 2, 3])
+    heads = kv * r.choice([1, 2, 3])
+    vdim = r.choice([32, 64, 96, 128]) if seed % 2 else r.choice([5, 12, 40])
+    layers = []
+    for li in range(r.choice([2, 3, 4])):
+        dim, vd = r.choice([(d, v) for d, v in MMA_SIZES if v == vdim] or [(r.choice([6, 20, 44]), vdim)])
+        if seed % 2 == 0:
+            dim = r.choice([6, 20, 44])
+        mix = r.random() < 0.7
+        h, g = (heads, kv) if mix else (r.choice([1, 2, 4]), 1)
+        v = vd if mix else r.choice([8, 32])
+        if r.random() < 0.5:
+            m = att(h, g, dim, v, dim ** -0.5 * r.choice([1.0, 3.0]), rot=r.choice([0, 2, dim // 2 // 2 * 2, dim]) or None, base=r.choice([100.0, 10000.0]), v_mix=mix)
+        else:
+            win = r.choice([None, 1, 7, 33, 64, 100])
+            m = att2(h, g, dim, v, r.choice([4.0, 12.0]) / dim, r.choice([1, 2, 3, 4]), window=win, keep=r.choice([0, 1, 9, 70]), v_mix=mix)   # unit-RMS q and k: |q.k| <= dim
+        layers.append((m, ff(r.choice([24, 64, 100]), r.choice([0.5, 2.0, 7.0])) if r.random() < 0.8 else None))
+    width = r.choice([64, 96, 128])
+    return model(layers, vocab=r.choice([50, 131, 256]), width=width, groups=r.choice([1, 2, 4, 8]), escale=r.choice([1.0, 4.0]))
+
+
+@pytest.mark.parametrize("seed", list(range(12)))
+def test_random_models_and_schedules(seed):
+    """fp32 and bf16 engines against the restatement on a random model: two requests, a long and a short one, fed in portions of
+    uneven size in one batch (the long one past the 64-token tiles of the prompt kernels), then decoded together."""
+    cfg = random_model(seed)
+    w = random_weights(cfg, seed=200 + seed)
+    for name in list(w):
+        if name.endswith("mix.talk"):
+            w[name] = (torch.eye(w[name].shape[0]) + 0.5 * torch.randn(w[name].shape, generator=torch.Generator().manual_seed(seed))).to(torch.bfloat16).float()
+    prompts = [tokens(cfg, 190, 300 + seed), tokens(cfg, 23, 400 + seed)]
+    refs = [ref_logits(cfg, w, p) for p in prompts]
+    for f32, bar in ((True, 1e-4), (False, BF16_BAR)):   # (fp32: some of these models are sharp enough to triple fp32 rounding)
+        with engine(cfg, w, f32=f32) as e:
+            sids = [e.seq_create(200), e.seq_create(32)]
+            done = [0, 0]
+            for step in ([(0, 70), (1, 2)], [(0, 97), (1, 11)], [(0, 3), (1, 1)], [(0, 1), (1, 2)]):
+                chunks, rows, base = [], [], 0
+                for rq, c in step:
+                    chunks.append(prompts[rq][done[rq]:done[rq] + c])
+                    rows += list(range(base, base + c))
+                    base += c
+                lg, _ = e.prefill_logits([sids[rq] for rq, _ in step], chunks, rows)
+                base = 0
+                for rq, c in step:
+                    assert err(lg[base:base + c], refs[rq][done[rq]:done[rq] + c]) < bar, "%s request %d at %d" % ("fp32" if f32 else "bf16", rq, done[rq])
+                    base += c
+                    done[rq] += c
+            while done[1] < len(prompts[1]):
+                e.decode_step(sids, in_tokens=[prompts[0][done[0]], prompts[1][done[1]]], want_output=False)
+                lg = e.get_logits(2)
+                for rq in (0, 1):
+                    assert err(lg[rq], refs[rq][done[rq]]) < bar, "%s decoded request %d at %d" % ("fp32" if f32 else "bf16", rq, done[rq])
+                    done[rq] += 1
+
+
 def test_greedy_generation_through_the_engine():
     cfg = cfg_a()
     w = random_weights(cfg, seed=19)
