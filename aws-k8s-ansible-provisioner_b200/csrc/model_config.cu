@@ -190,7 +190,9 @@ int kedasun_config(const Value& j, b2_config* c, b2_layer_spec* specs, int max_s
       return -22;
     }
     CFG_TRY(need_int(*m, "heads", where, &s.heads));
-    CFG_TRY(need_int(*m, "kv_heads", where, &s.kv_heads));
+    s.kv_heads = s.heads;   // no "kv_heads": every query head has its own keys and values
+    if (const Value* kh = m->find("kv_heads"))
+      if (kh->is_number()) s.kv_heads = (int)kh->as_int();
     CFG_TRY(need_int(*m, "dim", where, &s.dim));
     CFG_TRY(need_int(*m, "vdim", where, &s.vdim));
     CFG_TRY(need_float(*m, "scale", where, &s.scale));

@@ -344,8 +344,9 @@ def _fill_heads_spec(sp, layer: dict) -> None:
     m = layer["mixer"]
     conv = layer["type"] == "attention_2"
     sp.mixer = capi.MIXER_CONV_ATTENTION if conv else capi.MIXER_ATTENTION
-    for k in ("heads", "kv_heads", "dim", "vdim"):
+    for k in ("heads", "dim", "vdim"):
         setattr(sp, k, int(m[k]))
+    sp.kv_heads = int(m.get("kv_heads", m["heads"]))
     sp.scale, sp.kv_from, sp.v_mix = float(m["scale"]), -1, int(bool(m.get("v_mix")))
     if conv:
         sp.conv_taps = int(m["conv"])

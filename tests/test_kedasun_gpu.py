@@ -148,9 +148,9 @@ def test_each_mechanism_alone(name):
 
 
 def test_norm_pieces_wider_than_a_warp_keeps():
-    """One piece of 576 numbers (more than the 512 a warp holds in registers) beside a model whose pieces are 36 wide."""
+    """One piece of 1088 numbers (more than the 512 a warp holds in registers) beside a model whose pieces are 36 wide."""
     for groups in (1, 16):
-        cfg = model([(att(2, 1, 8, 8, 0.3, rot=4), ff(40)), (att2(2, 2, 8, 8, 1.1, 3, window=9, keep=2, v_mix=False), ff(24))], vocab=53, width=576, groups=groups)
+        cfg = model([(att(2, 1, 8, 8, 0.3, rot=4), ff(40)), (att2(2, 2, 8, 8, 1.1, 3, window=9, keep=2, v_mix=False), ff(24))], vocab=53, width=1088, groups=groups)
         w = random_weights(cfg, seed=80)
         toks = tokens(cfg, 30, 81)
         ref = ref_logits(cfg, w, toks)

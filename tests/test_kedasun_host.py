@@ -40,6 +40,14 @@ def test_registry_reads_the_layer_list(pkg, lib, tmp_path):
         assert bytes(sp) == bytes(specs[i])
         back = eng._layer_dict(sp)
         assert back["type"] == layer["type"] and back["mixer"].get("mask") == layer["mixer"].get("mask")
+    plain = small_cfg()     # no "kv_heads": as many as query heads; no "mask": no window; no "rot": nothing rotated
+    del plain["layers"][0]["mixer"]["kv_heads"], plain["layers"][0]["mixer"]["rot"], plain["layers"][1]["mixer"]["mask"]
+    (tmp_path / "config.json").write_text(json.dumps(plain))
+    assert lib.b2_config_from_dir(str(tmp_path).encode(), C.byref(c), specs, 8) == 0, lib.b2_last_error()
+    assert (specs[0].kv_heads, specs[0].rot_dims, specs[1].window, specs[1].keep_first) == (4, 0, 0, 0)
+    sp = capi.b2_layer_spec()
+    eng._fill_layer_spec(sp, plain["layers"][0])
+    assert bytes(sp) == bytes(specs[0])
     bad = small_cfg()
     bad["layers"][1]["mlp"] = {"kind": "moe"}
     (tmp_path / "config.json").write_text(json.dumps(bad))
