@@ -418,7 +418,7 @@ __global__ void __launch_bounds__(128 * HPC, 2) heads_attention_mma_kernel(const
   bf16* Vs = Ks + 2 * HM_KEYS * QS;                // [2][64][VS]
   pdl_wait();
   pdl_launch_dependents();
-  const PrefillTile tl = tiles[blockIdx.x];
+  const PrefillTile tl = tiles[gridDim.x - 1 - blockIdx.x];   // the tiles late in a sequence see the most keys: they start first
   if (tl.nrows <= 0) return;
   constexpr int NT = 128 * HPC;
   const int warp = (threadIdx.x >> 5) & 3, hl = threadIdx.x >> 7, lane = threadIdx.x & 31, gq = lane >> 2, tq = lane & 3;

@@ -125,7 +125,9 @@ __global__ void __launch_bounds__(128) embed_scaled_kernel(const int32_t* __rest
 // gain_next is given the norm in front of the next sublayer follows at once, x = norm(h) * gain_next (the pieces of both
 // norms are the same, so the warp that updated a piece normalises it).
 constexpr int GN_REG = 16;   // values of a piece a lane keeps in registers (pieces up to 512 wide)
-template <typename TX, bool ADD>
+// EARLY (steps of few tokens, where a launch is all latency): every operand is loaded before the first reduction -- one round trip
+// to memory instead of one per phase; prompt-sized steps load late and keep the registers for occupancy.
+template <typename TX, bool ADD, bool EARLY>
 __global__ void __launch_bounds__(128) group_norm_kernel(const float* __restrict__ src, const float* __restrict__ bias,
                                                          const float* __restrict__ gain, TX* __restrict__ x, float* __restrict__ h, int W,
                                                          int groups, float eps, const int32_t* __restrict__ rows,
@@ -140,11 +142,15 @@ __global__ void __launch_bounds__(128) group_norm_kernel(const float* __restrict
     const int o = gi * piece;
     if (piece <= 32 * GN_REG) {
       // the piece fits the warp's registers: every load of a pass is in flight at once, and nothing is read twice
-      float v[GN_REG], ss = 0.f;
+      float v[GN_REG], gv[GN_REG], hv[GN_REG], gn[GN_REG], ss = 0.f;
 #pragma unroll
       for (int k = 0; k < GN_REG; ++k) {
         const int i = lane + 32 * k;
-        v[k] = i < piece ? row[o + i] + (bias ? bias[o + i] : 0.f) : 0.f;
+        const bool in = i < piece;
+        v[k] = in ? row[o + i] + (bias ? bias[o + i] : 0.f) : 0.f;
+        gv[k] = (EARLY && in) ? gain[o + i] : 0.f;
+        hv[k] = (EARLY && ADD && in) ? h[(size_t)t * W + o + i] : 0.f;
+        gn[k] = (EARLY && ADD && in && gain_next != nullptr) ? gain_next[o + i] : 0.f;
         ss = fmaf(v[k], v[k], ss);
       }
       ss = warp_sum(ss);
@@ -154,9 +160,9 @@ __global__ void __launch_bounds__(128) group_norm_kernel(const float* __restrict
       for (int k = 0; k < GN_REG; ++k) {
         const int i = lane + 32 * k;
         if (i < piece) {
-          v[k] = v[k] * r * gain[o + i];
+          v[k] = v[k] * r * (EARLY ? gv[k] : gain[o + i]);
           if (ADD) {
-            v[k] += h[(size_t)t * W + o + i];
+            v[k] += EARLY ? hv[k] : h[(size_t)t * W + o + i];
             h[(size_t)t * W + o + i] = v[k];
             ss2 = fmaf(v[k], v[k], ss2);
           } else {
@@ -170,7 +176,7 @@ __global__ void __launch_bounds__(128) group_norm_kernel(const float* __restrict
 #pragma unroll
         for (int k = 0; k < GN_REG; ++k) {
           const int i = lane + 32 * k;
-          if (i < piece) x[(size_t)t * W + o + i] = (TX)(v[k] * r2 * gain_next[o + i]);
+          if (i < piece) x[(size_t)t * W + o + i] = (TX)(v[k] * r2 * (EARLY ? gn[k] : gain_next[o + i]));
         }
       }
       continue;
@@ -216,6 +222,7 @@ __global__ void __launch_bounds__(256) clamped_gate_kernel(const float* __restri
 
 }  // namespace
 
+constexpr int GN_EARLY_ROWS = 1024;
 static dim3 gn_grid(int T, int groups) { return dim3(T, T >= 1024 ? 1 : std::max(1, (groups + 3) / 4)); }
 
 int launch_embed_scaled(const int32_t* ids, const void* table, int table_f32, float scale, float* h, int T, int W, int vocab, cudaStream_t s) {
@@ -230,11 +237,11 @@ int launch_group_norm(const float* h, const float* gain, void* x, int x_f32, int
   if (T <= 0) return 0;
   B2_REQUIRE(groups >= 1 && W % groups == 0, "group_norm: width %d is not %d equal pieces", W, groups);
   if (x_f32)
-    B2_CUDA_OK(b2_launch(group_norm_kernel<float, false>, gn_grid(T, groups), dim3(128), 0, s, h, (const float*)nullptr, gain, (float*)x, (float*)nullptr, W, groups, eps, rows,
-                         (const float*)nullptr));
+    B2_CUDA_OK(b2_launch(T < GN_EARLY_ROWS ? group_norm_kernel<float, false, true> : group_norm_kernel<float, false, false>, gn_grid(T, groups), dim3(128), 0, s, h,
+                         (const float*)nullptr, gain, (float*)x, (float*)nullptr, W, groups, eps, rows, (const float*)nullptr));
   else
-    B2_CUDA_OK(b2_launch(group_norm_kernel<bf16, false>, gn_grid(T, groups), dim3(128), 0, s, h, (const float*)nullptr, gain, (bf16*)x, (float*)nullptr, W, groups, eps, rows,
-                         (const float*)nullptr));
+    B2_CUDA_OK(b2_launch(T < GN_EARLY_ROWS ? group_norm_kernel<bf16, false, true> : group_norm_kernel<bf16, false, false>, gn_grid(T, groups), dim3(128), 0, s, h,
+                         (const float*)nullptr, gain, (bf16*)x, (float*)nullptr, W, groups, eps, rows, (const float*)nullptr));
   return 0;
 }
 
@@ -244,9 +251,11 @@ int launch_group_norm_add(float* h, const float* y, const float* bias, const flo
   B2_REQUIRE(groups >= 1 && W % groups == 0, "group_norm: width %d is not %d equal pieces", W, groups);
   B2_REQUIRE((gain_next == nullptr) == (x_next == nullptr), "group_norm_add: the following norm needs its gain and its output");
   if (x_f32 || x_next == nullptr)
-    B2_CUDA_OK(b2_launch(group_norm_kernel<float, true>, gn_grid(T, groups), dim3(128), 0, s, y, bias, gain, (float*)x_next, h, W, groups, eps, (const int32_t*)nullptr, gain_next));
+    B2_CUDA_OK(b2_launch(T < GN_EARLY_ROWS ? group_norm_kernel<float, true, true> : group_norm_kernel<float, true, false>, gn_grid(T, groups), dim3(128), 0, s, y, bias, gain,
+                         (float*)x_next, h, W, groups, eps, (const int32_t*)nullptr, gain_next));
   else
-    B2_CUDA_OK(b2_launch(group_norm_kernel<bf16, true>, gn_grid(T, groups), dim3(128), 0, s, y, bias, gain, (bf16*)x_next, h, W, groups, eps, (const int32_t*)nullptr, gain_next));
+    B2_CUDA_OK(b2_launch(T < GN_EARLY_ROWS ? group_norm_kernel<bf16, true, true> : group_norm_kernel<bf16, true, false>, gn_grid(T, groups), dim3(128), 0, s, y, bias, gain,
+                         (bf16*)x_next, h, W, groups, eps, (const int32_t*)nullptr, gain_next));
   return 0;
 }
 
