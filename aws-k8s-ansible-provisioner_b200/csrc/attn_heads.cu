@@ -57,6 +57,13 @@ __device__ __forceinline__ void pair_cos_sin(int pos, int i, int dims, float bas
   *s = (float)sd;
 }
 
+// Element index of (slot, key/value head, dim) in the page layout of the GQA kernels (attn_decode.cu, attn_prefill_tc.cu): pages of 16
+// tokens, [page][kv_head][16][128], the 16-byte chunks of a token row XOR-swizzled by the row (kv_swizzled_chunk).
+__device__ __forceinline__ size_t swizzled_index(int slot, int kvh, int kv_heads, int d) {
+  const int page = slot >> 4, r = slot & 15;
+  return (((size_t)page * kv_heads + kvh) * 16 + r) * 128 + (size_t)kv_swizzled_chunk(r, d >> 3) * 8 + (d & 7);
+}
+
 // A CTA takes `upc` heads of one token, counted through the query heads, then the key heads, then the value heads, one warp per
 // head at a time: all of them for prompt-sized steps (the token's cosines and sines are formed once), four when the step has few
 // tokens.  proj [T][ld] fp32: q (heads * dim) | k (kv_heads * dim) | v (kv_heads * vdim) | anything else.
@@ -66,7 +73,8 @@ __global__ void __launch_bounds__(128) heads_finish_kernel(const float* __restri
                                                            const int32_t* __restrict__ row_seq, const int32_t* __restrict__ row_first,
                                                            const int32_t* __restrict__ positions, const int32_t* __restrict__ slots,
                                                            int vmix_mode, const float* __restrict__ vmix_lambda, float* __restrict__ v_first,
-                                                           float* __restrict__ q_out, TC* __restrict__ k_cache, TC* __restrict__ v_cache, int upc) {
+                                                           float* __restrict__ q_out, TC* __restrict__ k_cache, TC* __restrict__ v_cache, int upc,
+                                                           bf16* __restrict__ q_bf16) {
   extern __shared__ float sm[];
   pdl_wait();
   pdl_launch_dependents();
@@ -119,7 +127,8 @@ __global__ void __launch_bounds__(128) heads_finish_kernel(const float* __restri
         float v = y[i];
         if (vmix_mode == 1) vf[i] = v;
         else if (vmix_mode == 2) v = (1.0f - lam) * v + lam * vf[i];
-        stf(vr + i, v);
+        if (g.swizzled) stf(v_cache + swizzled_index(slot, u - g.heads - g.kv_heads, g.kv_heads, i), v);
+        else stf(vr + i, v);
       }
       continue;
     }
@@ -143,8 +152,16 @@ __global__ void __launch_bounds__(128) heads_finish_kernel(const float* __restri
         b = rb;
       }
       if (is_q) {
-        qo[2 * p] = a;
-        if (two) qo[2 * p + 1] = b;
+        if (q_bf16 != nullptr) {   // the GQA tensor-core kernels take bf16 queries
+          *reinterpret_cast<uint32_t*>(q_bf16 + (size_t)t * nq + c0 + 2 * p) = pack_bf16x2(a, b);
+        } else {
+          qo[2 * p] = a;
+          if (two) qo[2 * p + 1] = b;
+        }
+      } else if (g.swizzled) {
+        const size_t at = swizzled_index(slot, u - g.heads, g.kv_heads, 2 * p);
+        stf(k_cache + at, a);
+        stf(k_cache + at + 1, b);
       } else {
         stf(kr + 2 * p, a);
         if (two) stf(kr + 2 * p + 1, b);
@@ -686,8 +703,9 @@ int launch_attention_t(const float* q, const void* k, const void* v, const Heads
 int launch_heads_finish(const float* proj, int ld, const HeadsGeom& g, const float* bias, const float* conv_w, float* ring,
                         const int32_t* row_seq, const int32_t* row_first, const int32_t* row_end, const int32_t* positions,
                         const int32_t* slots, int vmix_mode, const float* vmix_lambda, float* v_first, float* q_out, void* k_cache,
-                        void* v_cache, int cache_f32, int T, cudaStream_t s) {
+                        void* v_cache, int cache_f32, int T, cudaStream_t s, void* q_bf16) {
   if (T <= 0) return 0;
+  B2_REQUIRE(!g.swizzled || (!cache_f32 && g.dim == 128 && g.vdim == 128 && q_bf16 != nullptr), "heads_finish: the swizzled page layout is bf16, 128 wide");
   B2_REQUIRE(g.rot_dims >= 0 && g.rot_dims <= g.dim && g.rot_dims % 2 == 0, "heads_finish: rot dims %d must be even and <= dim %d", g.rot_dims,
              g.dim);
   B2_REQUIRE(g.conv_taps == 0 || (conv_w && ring && row_seq && row_first && row_end), "heads_finish: the convolution needs its weights and state");
@@ -701,12 +719,12 @@ int launch_heads_finish(const float* proj, int ld, const HeadsGeom& g, const flo
     auto kern = heads_finish_kernel<float>;
     if (smem > 48 * 1024) B2_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     B2_CUDA_OK(b2_launch(kern, fgrid, dim3(128), smem, s, proj, ld, g, bias, conv_w, (const float*)ring, row_seq, row_first, positions, slots,
-                         vmix_mode, vmix_lambda, v_first, q_out, (float*)k_cache, (float*)v_cache, upc));
+                         vmix_mode, vmix_lambda, v_first, q_out, (float*)k_cache, (float*)v_cache, upc, (bf16*)nullptr));
   } else {
     auto kern = heads_finish_kernel<bf16>;
     if (smem > 48 * 1024) B2_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     B2_CUDA_OK(b2_launch(kern, fgrid, dim3(128), smem, s, proj, ld, g, bias, conv_w, (const float*)ring, row_seq, row_first, positions, slots,
-                         vmix_mode, vmix_lambda, v_first, q_out, (bf16*)k_cache, (bf16*)v_cache, upc));
+                         vmix_mode, vmix_lambda, v_first, q_out, (bf16*)k_cache, (bf16*)v_cache, upc, (bf16*)q_bf16));
   }
   if (g.conv_taps > 1)
     B2_CUDA_OK(b2_launch(conv_tail_store_kernel, dim3(T), dim3(128), 0, s, proj, ld, C, g.conv_taps, bias, ring, row_seq, row_end, positions, slots));

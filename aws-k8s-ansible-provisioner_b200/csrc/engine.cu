@@ -91,6 +91,8 @@ struct ListLayer {
   int nk = 0, nv = 0;         // kv_heads * dim, kv_heads * vdim
   int v_region = -1;          // cache region of the values (cache_region holds the keys)
   int vmix_mode = 0;          // 0 no value mixing, 1 the layer supplies the first values, 2 it blends with them
+  bool gqa_tc = false;        // bf16, 128-wide heads in groups of two, plain causal softmax: the layer's cache has the GQA kernels' page
+                              // layout and attention runs on attn_prefill_tc.cu / attn_decode.cu
   float *gain1b = nullptr, *gain2b = nullptr, *qkv_bias = nullptr, *o_bias = nullptr, *conv_w = nullptr, *talk = nullptr, *vmix = nullptr;
   float* conv_ring = nullptr; // [sequence slots][taps][q | k | v channels], row = position mod taps: the projected rows a sequence's next convolutions need
 };
@@ -298,6 +300,7 @@ struct b2_engine {
   // per-head attention (Kedasun): fp32 queries, the first value-mixing layer's values of the step's tokens, the per-head sums
   // that weight mixing combines; and, per token row of the step, its sequence slot and the row range of its portion
   float *l_q = nullptr, *l_vfirst = nullptr, *l_cross = nullptr;
+  bf16* l_qb = nullptr;              // bf16 queries of the layers the GQA kernels serve
   int32_t *d_row_seq = nullptr, *d_row_first = nullptr, *d_row_end = nullptr;
   bool l_has_state = false;          // some layer keeps per-sequence state besides the cache (convolution rings)
   float* l_attn_scratch = nullptr;   // key splits of a decode step's latent attention
@@ -357,7 +360,9 @@ struct KL {
 
 // Models with one query head per kv head run through the GQA-2 kernels with an all-zero partner head after every real one;
 // the tcgen05 prefill attention then pairs two 64-token tiles per CTA instead of (real, zero) heads.
-static bool prefill_tile_pairs(const b2_engine* e) { return e->prefill_tc && e->qhead_step == 2 && e->cfg.arch != B2_ARCH_OPT && e->prefill_pairs; }
+static bool prefill_tile_pairs(const b2_engine* e) {
+  return e->prefill_tc && e->qhead_step == 2 && e->cfg.arch != B2_ARCH_OPT && !list_arch(e->cfg.arch) && e->prefill_pairs;
+}
 
 int bucket_batch(int B) {
   static const int bk[] = {1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256, 384, 512};
@@ -1060,7 +1065,7 @@ int forward_heads_list(b2_engine* e, int T, int ntiles, int nlast) {
     const b2_layer_spec& sp = L.sp;
     const bool conv = sp.mixer == B2_MIXER_CONV_ATTENTION;
     HeadsGeom g{sp.heads, sp.kv_heads, sp.dim, sp.vdim, sp.rot_dims, sp.rot_base, sp.scale, c.rms_eps, conv ? sp.conv_taps : 0, conv ? 1 : 0,
-                conv ? 1 : 0, KEDASUN_SLOPE_EXP, sp.window, sp.keep_first, conv ? 1 : 0};
+                conv ? 1 : 0, KEDASUN_SLOPE_EXP, sp.window, sp.keep_first, conv ? 1 : 0, L.gqa_tc ? 1 : 0};
     char* kc = e->regions[L.cache_region].base;
     char* vc = e->regions[L.v_region].base;
     const bool has_ff = sp.ff == B2_FF_CLAMPED_GATED;
@@ -1076,9 +1081,20 @@ int forward_heads_list(b2_engine* e, int T, int ntiles, int nlast) {
     {
       KL k(e, B2K_ROPE_KV);
       if (!k.skip()) B2_TRY(launch_heads_finish(e->l_qd, L.nqd, g, L.qkv_bias, L.conv_w, L.conv_ring, e->d_row_seq, e->d_row_first, e->d_row_end,
-                                                e->d_positions, e->d_slots, L.vmix_mode, L.vmix, e->l_vfirst, e->l_q, kc, vc, f, T, st));
+                                                e->d_positions, e->d_slots, L.vmix_mode, L.vmix, e->l_vfirst, e->l_q, kc, vc, f, T, st,
+                                                L.gqa_tc ? e->l_qb : nullptr));
     }
-    {
+    if (L.gqa_tc) {   // the framework's GQA kernels: tcgen05 for prompt portions, the page-balanced stream for decode steps
+      KL k(e, ntiles > 0 ? B2K_MISC : B2K_ATTN_DECODE);
+      if (!k.skip()) {
+        if (ntiles > 0)
+          B2_TRY(launch_attn_prefill_tc(e->l_qb, (const bf16*)kc, (const bf16*)vc, e->num_blocks, e->d_block_table, e->bt_stride, e->d_tiles, ntiles,
+                                        (bf16*)e->l_av, sp.heads, sp.kv_heads, 128, c.block_size, st, sp.scale, 0, 0));
+        else
+          B2_TRY(launch_attn_decode(e->l_qb, (const bf16*)kc, (const bf16*)vc, e->d_block_table, e->bt_stride, e->d_seq_lens, e->attn_scratch, (bf16*)e->l_av, T,
+                                    sp.heads, sp.kv_heads, 128, c.block_size, st, sp.scale, 0, 0));
+      }
+    } else {
       KL k(e, ntiles > 0 ? B2K_MISC : B2K_ATTN_DECODE);
       if (!k.skip()) B2_TRY(launch_heads_attention(e->l_q, kc, vc, f, g, e->d_block_table, e->bt_stride, c.block_size, tiles, ntiles, e->d_positions,
                                                    e->d_seq_lens, conv ? (void*)e->l_cross : e->l_av, conv ? 1 : f, T, st));
@@ -1663,7 +1679,7 @@ int heads_engine_alloc(b2_engine* e) {
   B2_TRY(xalloc(&e->l_head, (size_t)c.vocab * W));
   B2_TRY(falloc(&e->l_final_gain, W));
   e->ll.resize(c.num_layers);
-  size_t max_nqd = 1, max_nq = 1, max_nv = 1, max_hv = 1, max_cross = 0, max_ff = 1;
+  size_t max_nqd = 1, max_nq = 1, max_nv = 1, max_hv = 1, max_cross = 0, max_ff = 1, gqa_scratch = 0;
   int first_vmix = -1;
   for (int l = 0; l < c.num_layers; ++l) {
     ListLayer& L = e->ll[l];
@@ -1708,6 +1724,10 @@ int heads_engine_alloc(b2_engine* e) {
       B2_TRY(xalloc(&L.down, W * sp.ff_dim));
       max_ff = std::max(max_ff, (size_t)sp.ff_dim);
     }
+    static const bool use_gqa_tc = [] { const char* v = getenv("B2_HEADS_GQA_TC"); return !(v && *v == '0'); }();
+    L.gqa_tc = use_gqa_tc && !e->f32 && !conv && sp.dim == 128 && sp.vdim == 128 && sp.heads == 2 * sp.kv_heads && sp.window == 0 &&
+               c.block_size == 16 && (c.max_model_len + 15) / 16 <= 1024 && (long)bucket_batch(c.max_seqs) * sp.kv_heads <= 4096;
+    if (L.gqa_tc) gqa_scratch = std::max(gqa_scratch, attn_decode_scratch_floats(bucket_batch(c.max_seqs), sp.heads, sp.kv_heads, 128));
     max_nqd = std::max(max_nqd, (size_t)L.nqd);
     max_nq = std::max(max_nq, (size_t)L.nq);
     max_nv = std::max(max_nv, (size_t)L.nv);
@@ -1729,6 +1749,12 @@ int heads_engine_alloc(b2_engine* e) {
   B2_TRY(dalloc(&e->l_q, Tc * max_nq));
   B2_TRY(dalloc(&e->l_vfirst, Tc * max_nv));
   if (max_cross > 0) B2_TRY(dalloc(&e->l_cross, Tc * max_cross));
+  if (gqa_scratch > 0) {
+    B2_TRY(dalloc(&e->l_qb, Tc * max_nq));
+    e->attn_scratch_floats = gqa_scratch;
+    B2_TRY(dalloc(&e->attn_scratch, gqa_scratch));
+    B2_CUDA_OK(cudaMemset(e->attn_scratch, 0, gqa_scratch * sizeof(float)));   // arrival counters start at zero
+  }
   B2_TRY(dalloc(&e->l_mix, Tc * W));
   B2_TRY(dalloc(&e->l_y, Tc * 2 * max_ff));
   B2_TRY(dalloc(&e->l_logits, (size_t)e->l_rows_cap * c.vocab));
@@ -2535,7 +2561,7 @@ extern "C" void b2_engine_free(b2_engine* e) {
   F(e->partial2); F(e->attn_scratch2); F(e->ssq);
   F(e->l_embed); F(e->l_head); F(e->l_embed_gain); F(e->l_final_gain); F(e->l_pool); F(e->l_h); F(e->l_qd); F(e->l_qrot); F(e->l_qabs);
   F(e->l_xperm); F(e->l_upf); if (e->h_offsets) cudaFreeHost(e->h_offsets);
-  F(e->l_q); F(e->l_vfirst); F(e->l_cross); F(e->d_row_seq); F(e->d_row_first); F(e->d_row_end);
+  F(e->l_q); F(e->l_vfirst); F(e->l_cross); F(e->l_qb); F(e->d_row_seq); F(e->d_row_first); F(e->d_row_end);
   F(e->l_mix); F(e->l_y); F(e->l_rw); F(e->l_logits); F(e->l_x1); F(e->l_x2); F(e->l_qnope); F(e->l_olat); F(e->l_av); F(e->l_act); F(e->l_xl);
   F(e->l_attn_scratch); F(e->l_idx); F(e->l_offsets); F(e->l_slot_token); F(e->l_pair_slot); F(e->l_tile_group); F(e->l_tile_row0); F(e->l_ntiles); F(e->dbg_hidden_f32);
   for (auto& L : e->ll) {

@@ -277,6 +277,8 @@ struct HeadsGeom {
   float slope_exp;
   int window, keep_first;           // window > 0: key j is seen from i when i - j < window or j < keep_first
   int cross;                        // 1: every query head's weights are applied to the values of every key/value head (for talk_gate)
+  int swizzled;                     // 1: K and V rows go into the page layout of the GQA kernels (bf16, 128 wide, kv_swizzled_chunk) and the
+                                    //    queries out as bf16, so that attn_decode.cu / attn_prefill_tc.cu serve the layer
 };
 // proj [T][ld] fp32 = q | k | v (| more) of the fused projection.  bias [heads*dim + kv_heads*(dim+vdim)] or null; conv_w [channels][taps];
 // ring [sequence slots][taps][channels] fp32 (row = position mod taps); row_seq / row_first / row_end [T]: the token's sequence slot and the first row / one past
@@ -285,7 +287,7 @@ struct HeadsGeom {
 int launch_heads_finish(const float* proj, int ld, const HeadsGeom& g, const float* bias, const float* conv_w, float* ring,
                         const int32_t* row_seq, const int32_t* row_first, const int32_t* row_end, const int32_t* positions,
                         const int32_t* slots, int vmix_mode, const float* vmix_lambda, float* v_first, float* q_out, void* k_cache,
-                        void* v_cache, int cache_f32, int T, cudaStream_t s);
+                        void* v_cache, int cache_f32, int T, cudaStream_t s, void* q_bf16 = nullptr);
 // tiles == null: decode form (row i is the newest token of block-table row i at positions[i]; seq_lens[i] == 0 rows give zeros).
 // out [T][heads][vdim] (fp32 or bf16), or with g.cross [T][heads][kv_heads*vdim] fp32.
 int launch_heads_attention(const float* q, const void* k_cache, const void* v_cache, int cache_f32, const HeadsGeom& g,
